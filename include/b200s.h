@@ -1,0 +1,171 @@
+/*
+ * b200s — Strassen / Strassen-Winograd / dense matrix multiplication for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libb200s.so. Plain pointers and sizes only; every pointer named "device" is a CUDA
+ * device pointer of the current device, every stream is a cudaStream_t passed as void*.
+ * All functions return a b200s_status (0 = success, negative = error); none throws, aborts
+ * or synchronises the device unless its comment says so.
+ *
+ * The reference project (vmad18/strassen-triton) is pure Python and has no FFI of its own:
+ * its boundary for this path is a set of module-level functions taking torch tensors. Each
+ * entry point below names the reference function(s) whose arithmetic it carries; the Python
+ * modules of the same names in this repository bind these entry points with ctypes.
+ */
+#ifndef B200S_H_
+#define B200S_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200s_status {
+  B200S_OK = 0,
+  B200S_ERR_NULL_POINTER = -1,
+  B200S_ERR_BAD_SHAPE = -2,     /* non-positive extent, or extent not divisible as the depth needs */
+  B200S_ERR_BAD_STRIDE = -3,    /* leading dimension too small or not a multiple of 16 bytes */
+  B200S_ERR_BAD_ALIGNMENT = -4, /* base pointer not 16-byte aligned */
+  B200S_ERR_BAD_DTYPE = -5,
+  B200S_ERR_BAD_ALGO = -6,
+  B200S_ERR_BAD_DEPTH = -7,
+  B200S_ERR_WORKSPACE_TOO_SMALL = -8,
+  B200S_ERR_CUDA = -9,          /* a CUDA runtime/driver call failed; see b200s_last_cuda_error */
+  B200S_ERR_NO_DEVICE = -10,    /* no sm_100 device is current */
+  B200S_ERR_DEVICE_TIMEOUT = -11, /* a kernel gave up on a bounded wait (read by b200s_device_status) */
+  B200S_ERR_TUNER_IO = -12,
+  B200S_ERR_TOO_LARGE = -13     /* problem exceeds the fixed capacity of a no-allocation entry point */
+} b200s_status;
+
+typedef enum b200s_dtype { B200S_BF16 = 0, B200S_FP16 = 1, B200S_FP32 = 2 } b200s_dtype;
+
+/* Which operand dimension is contiguous in memory. */
+typedef enum b200s_major {
+  B200S_K_MAJOR = 0, /* the contraction dimension K is contiguous: A stored M x K, B stored N x K */
+  B200S_MN_MAJOR = 1 /* the outer dimension is contiguous: A stored K x M, B stored K x N */
+} b200s_major;
+
+typedef enum b200s_algo {
+  B200S_ALGO_AUTO = 0,    /* tuner table decides algorithm and depth */
+  B200S_ALGO_DENSE = 1,   /* plain tensor-core GEMM, depth ignored */
+  B200S_ALGO_CLASSIC = 2, /* Strassen's 7 products, 10 pre-additions, 8 post-additions */
+  B200S_ALGO_WINOGRAD = 3 /* Strassen-Winograd form: 7 products, 8 + 7 additions */
+} b200s_algo;
+
+/* How fp32 inputs reach the tensor cores. */
+typedef enum b200s_precision {
+  B200S_PREC_TF32 = 0,  /* one TF32 pass (10-bit mantissa operands), what torch does with allow_tf32 */
+  B200S_PREC_3XTF32 = 1 /* split each operand into hi+lo TF32 parts, three passes, ~fp32 accuracy */
+} b200s_precision;
+
+/*
+ * One matrix product C[b] (+)= A[b] . B[b], b = 0..batch-1, with A logically M x K and
+ * B logically K x N. Leading dimensions and batch strides are in ELEMENTS.
+ *   a_major == K_MAJOR : A[b](m,k) = A[b*strideA + m*lda + k]     (row-major M x K)
+ *   a_major == MN_MAJOR: A[b](m,k) = A[b*strideA + k*lda + m]     (row-major K x M, e.g. X.T)
+ *   b_major == MN_MAJOR: B[b](k,n) = B[b*strideB + k*ldb + n]     (row-major K x N)
+ *   b_major == K_MAJOR : B[b](k,n) = B[b*strideB + n*ldb + k]     (row-major N x K, e.g. weight.T)
+ *   C[b](m,n) = C[b*strideC + m*ldc + n], always row-major.
+ */
+typedef struct b200s_problem {
+  int64_t M, N, K;
+  int64_t batch;
+  int64_t lda, ldb, ldc;
+  int64_t strideA, strideB, strideC;
+  int32_t a_major;    /* b200s_major */
+  int32_t b_major;    /* b200s_major */
+  int32_t in_dtype;   /* b200s_dtype of A and B */
+  int32_t out_dtype;  /* b200s_dtype of C */
+  int32_t algo;       /* b200s_algo */
+  int32_t depth;      /* recursion levels 0..2, or -1 = tuner table decides */
+  int32_t beta;       /* 0: C = A.B   1: C += A.B */
+  int32_t prod_dtype; /* dtype the 7^depth sub-products are stored in between the GEMM and the
+                         recombination: B200S_FP32, or the input dtype (the reference's rounding
+                         point: torch.mm returns the input dtype). -1 = same as in_dtype */
+  int32_t precision;  /* b200s_precision, used when in_dtype is fp32 */
+  int32_t tile_variant; /* GEMM tile shape: 0 = library default, 1 = one CTA per 128x256 tile,
+                         2 = a CTA pair per 256x256 tile (tcgen05 cta_group::2) */
+} b200s_problem;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int b200s_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* b200s_status_string(int status);
+
+/* Text of the last CUDA error seen by the calling host thread ("" if none). */
+const char* b200s_last_cuda_error(void);
+
+/*
+ * Bytes of device scratch b200s_matmul needs for this problem after algo/depth resolution
+ * (0 for a dense product). Scratch holds the 7^depth pre-added operand blocks of A and B and the
+ * 7^depth sub-products: the temporaries S1..S10 and M1..M7 of
+ * fixed_strassen_fp32_agg.py:87-113 and :38-44.
+ */
+int b200s_workspace_bytes(const b200s_problem* p, size_t* bytes_out);
+
+/*
+ * C (+)= A . B on `stream`. Replaces, on the device, the arithmetic of
+ *   fixed_strassen_fp32_agg.py:13-56   _strassen_base                (algo classic, depth 1)
+ *   fixed_strassen_fp32_agg.py:59-125  strassen_matmul_n_layers      (classic, depth 2)
+ *   fixed_strassen.py:12-126           the same-dtype twins
+ *   strassen.py:697-812                _strassen_base / strassen_matmul_two_layers
+ *   strassen.py:66-88,195-213,674-693  run_matmul_fp32_accum / run_strassen / run_strassen2 (beta = 1)
+ *   strassen_2_layer.py:7-15           run_strassen_2_layer_fp32_accum (beta = 1, depth 2)
+ *   strassen_no_tuning.py:536-556      run_winograd_strassen          (algo winograd, beta = 1)
+ * Operand blocks are summed in fp32 from the original blocks and rounded once to the input
+ * dtype; products accumulate in fp32 on the tensor cores; recombination across all levels sums
+ * in fp32 and rounds once to out_dtype.
+ * `workspace` may be NULL when b200s_workspace_bytes reports 0. Asynchronous: returns after
+ * enqueuing the kernels.
+ */
+int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_device, void* C_device,
+                 void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
+ * The algorithm and depth b200s_matmul will use for p (resolves AUTO / -1 through the tuner
+ * table; clamps depth to what the extents allow). Replaces the hand-chosen `depth=` arguments and
+ * the triton.autotune config lists of strassen.py:9-30,93-114,218-236.
+ */
+int b200s_resolve(const b200s_problem* p, int32_t* algo_out, int32_t* depth_out);
+
+/*
+ * Tuner table: measured (M,N,K,in_dtype) -> (algo, depth) entries; lookups pick the entry whose
+ * log-volume is nearest and fall back to a dense product below the smallest recorded crossover.
+ * The table is process-wide, guarded by a mutex. File format: one entry per line,
+ * "M N K in_dtype algo depth".
+ */
+int b200s_tuner_clear(void);
+int b200s_tuner_record(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t algo, int32_t depth);
+int b200s_tuner_load(const char* path);
+int b200s_tuner_save(const char* path);
+int b200s_tuner_lookup(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t* algo_out,
+                       int32_t* depth_out);
+
+/*
+ * Reads (device -> host, synchronising `stream`) and clears the per-device status word that
+ * kernels set when a bounded wait ran out. *status_out is B200S_OK or B200S_ERR_DEVICE_TIMEOUT,
+ * *detail_out the role code of the waiter that gave up.
+ */
+int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out);
+
+/* Number of kernels this library has launched in the calling process (for benchmarks' accounting). */
+int64_t b200s_launch_count(void);
+
+/*
+ * Stand-alone passes of the Strassen pipeline, exposed for tests and profiling.
+ * b200s_preadd: writes the 7^depth operand blocks of one side (side 0 = A, 1 = B) into `out`
+ *   (block p at out + p * rows_blk * cols_blk elements, same major as the input).
+ * b200s_combine: reads 7^depth product blocks (Mb x Nb each, row-major, prod_dtype) and writes
+ *   or accumulates C.
+ * They carry the additions of fixed_strassen_fp32_agg.py:87-96 and :115-118.
+ */
+int b200s_preadd(const b200s_problem* p, int side, const void* X_device, void* out_device, void* stream);
+int b200s_combine(const b200s_problem* p, const void* products_device, void* C_device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200S_H_ */

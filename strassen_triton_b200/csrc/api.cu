@@ -1,0 +1,454 @@
+// C ABI of libb200s.so: argument validation, algorithm/depth resolution through the tuner
+// table, workspace layout, and the launch sequence pre-add(A), pre-add(B), grouped GEMM,
+// recombination. Nothing here touches host copies of the matrices; there is no CPU path.
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.h"
+#include "schedule.h"
+
+namespace b200s {
+
+namespace {
+
+thread_local char g_cuda_error[512] = "";
+std::atomic<int64_t> g_launches{0};
+
+struct DeviceState {
+  bool ready = false;
+  bool ok = false;
+  int sms = 0;
+  uint32_t* status = nullptr;
+};
+std::mutex g_dev_mu;
+DeviceState g_dev[64];
+
+DeviceState* current_device_state() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  DeviceState& s = g_dev[dev];
+  if (!s.ready) {
+    s.ready = true;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return &s;
+    if (prop.major != 10) return &s;  // tcgen05 / TMEM kernels: sm_100 only
+    s.sms = prop.multiProcessorCount;
+    void* ptr = nullptr;
+    if (cudaMalloc(&ptr, 2 * sizeof(uint32_t)) != cudaSuccess) return &s;
+    if (cudaMemset(ptr, 0, 2 * sizeof(uint32_t)) != cudaSuccess) return &s;
+    s.status = static_cast<uint32_t*>(ptr);
+    s.ok = true;
+  }
+  return &s;
+}
+
+// ---- tuner table ---------------------------------------------------------------------------
+struct TunerEntry {
+  int64_t M, N, K;
+  int32_t in_dtype, algo, depth;
+};
+std::mutex g_tuner_mu;
+std::vector<TunerEntry> g_tuner;
+
+double log_volume(int64_t M, int64_t N, int64_t K) {
+  return std::log2(static_cast<double>(M)) + std::log2(static_cast<double>(N)) + std::log2(static_cast<double>(K));
+}
+
+// Built-in choice when the table holds nothing for the dtype: dense below a cube of
+// kDefaultCrossover, one Strassen level above it, two above twice that.
+constexpr int64_t kDefaultCrossover = 8192;
+
+void default_choice(int64_t M, int64_t N, int64_t K, int32_t* algo, int32_t* depth) {
+  const double v = log_volume(M, N, K);
+  const double c1 = 3.0 * std::log2(static_cast<double>(kDefaultCrossover));
+  if (v < c1) {
+    *algo = B200S_ALGO_DENSE, *depth = 0;
+  } else if (v < c1 + 3.0) {
+    *algo = B200S_ALGO_CLASSIC, *depth = 1;
+  } else {
+    *algo = B200S_ALGO_CLASSIC, *depth = 2;
+  }
+}
+
+bool valid_dtype(int d) { return d == B200S_BF16 || d == B200S_FP16 || d == B200S_FP32; }
+
+// Largest depth <= want for which every extent splits into 2^depth blocks whose contiguous
+// runs are whole 16-byte vectors.
+int feasible_depth(const b200s_problem& p, int want) {
+  int d = want;
+  while (d > 0) {
+    const int64_t q = (int64_t{1} << d) * 8;
+    if (p.M % q == 0 && p.N % q == 0 && p.K % q == 0) break;
+    --d;
+  }
+  return d;
+}
+
+struct Plan {
+  int algo, depth, prod_dtype;
+  int64_t np;               // 7^depth
+  int64_t Mb, Nb, Kb;       // block extents
+  size_t sa_bytes, sb_bytes, mp_bytes;
+  size_t total_bytes;
+};
+
+size_t round256(size_t x) { return (x + 255) & ~size_t{255}; }
+
+int make_plan(const b200s_problem* p, Plan* plan) {
+  if (!p) return B200S_ERR_NULL_POINTER;
+  if (p->M <= 0 || p->N <= 0 || p->K <= 0 || p->batch <= 0) return B200S_ERR_BAD_SHAPE;
+  if (!valid_dtype(p->in_dtype) || !valid_dtype(p->out_dtype)) return B200S_ERR_BAD_DTYPE;
+  if (p->a_major != B200S_K_MAJOR && p->a_major != B200S_MN_MAJOR) return B200S_ERR_BAD_STRIDE;
+  if (p->b_major != B200S_K_MAJOR && p->b_major != B200S_MN_MAJOR) return B200S_ERR_BAD_STRIDE;
+  if (p->algo < B200S_ALGO_AUTO || p->algo > B200S_ALGO_WINOGRAD) return B200S_ERR_BAD_ALGO;
+  if (p->depth < -1 || p->depth > 2) return B200S_ERR_BAD_DEPTH;
+  if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
+  const int64_t a_cols = p->a_major == B200S_K_MAJOR ? p->K : p->M;
+  const int64_t b_cols = p->b_major == B200S_K_MAJOR ? p->K : p->N;
+  if (p->lda < a_cols || p->ldb < b_cols || p->ldc < p->N) return B200S_ERR_BAD_STRIDE;
+
+  int32_t algo = p->algo, depth = p->depth;
+  if (algo == B200S_ALGO_AUTO || depth < 0) {
+    int32_t ta, td;
+    b200s_tuner_lookup(p->M, p->N, p->K, p->in_dtype, &ta, &td);
+    if (algo == B200S_ALGO_AUTO) {
+      algo = ta;
+      if (depth < 0) depth = td;
+    } else if (depth < 0) {
+      depth = (algo == B200S_ALGO_DENSE) ? 0 : (td > 0 ? td : 1);
+    }
+    if (algo == B200S_ALGO_DENSE) depth = 0;
+    if (algo != B200S_ALGO_DENSE && depth == 0) algo = B200S_ALGO_DENSE;
+  }
+  if (algo == B200S_ALGO_DENSE) depth = 0;
+  if (algo != B200S_ALGO_DENSE) {
+    if (p->algo != B200S_ALGO_AUTO && p->depth > 0) {
+      // An explicit request must be met exactly.
+      if (feasible_depth(*p, depth) != depth) return B200S_ERR_BAD_SHAPE;
+    } else {
+      depth = feasible_depth(*p, depth);
+    }
+    if (depth == 0) algo = B200S_ALGO_DENSE;
+  }
+
+  plan->algo = algo;
+  plan->depth = depth;
+  int pd = p->prod_dtype < 0 ? p->in_dtype : p->prod_dtype;
+  if (!valid_dtype(pd)) return B200S_ERR_BAD_DTYPE;
+  if (p->in_dtype == B200S_FP32) pd = B200S_FP32;
+  plan->prod_dtype = pd;
+  plan->np = sched::ipow(7, depth);
+  const int64_t div = int64_t{1} << depth;
+  plan->Mb = p->M / div;
+  plan->Nb = p->N / div;
+  plan->Kb = p->K / div;
+  if (depth == 0) {
+    plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = plan->total_bytes = 0;
+    return B200S_OK;
+  }
+  const size_t es = dtype_size(p->in_dtype), ps = dtype_size(pd);
+  const size_t nb = static_cast<size_t>(p->batch) * static_cast<size_t>(plan->np);
+  plan->sa_bytes = round256(nb * plan->Mb * plan->Kb * es);
+  plan->sb_bytes = round256(nb * plan->Kb * plan->Nb * es);
+  plan->mp_bytes = round256(nb * plan->Mb * plan->Nb * ps);
+  plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes;
+  return B200S_OK;
+}
+
+}  // namespace
+
+void note_cuda_error(cudaError_t e, const char* where) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+                cudaGetErrorString(e));
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+uint32_t* device_status_words() {
+  DeviceState* s = current_device_state();
+  return (s && s->ok) ? s->status : nullptr;
+}
+int sm_count() {
+  DeviceState* s = current_device_state();
+  return (s && s->ok) ? s->sms : 0;
+}
+
+}  // namespace b200s
+
+using namespace b200s;
+
+extern "C" {
+
+int b200s_version(void) { return 100; }
+
+const char* b200s_status_string(int status) {
+  switch (status) {
+    case B200S_OK: return "ok";
+    case B200S_ERR_NULL_POINTER: return "null pointer argument";
+    case B200S_ERR_BAD_SHAPE: return "bad shape: non-positive extent, or extents not divisible as the requested depth needs";
+    case B200S_ERR_BAD_STRIDE: return "bad stride or major: leading dimension too small or not a multiple of 16 bytes";
+    case B200S_ERR_BAD_ALIGNMENT: return "base pointer not 16-byte aligned";
+    case B200S_ERR_BAD_DTYPE: return "unsupported dtype";
+    case B200S_ERR_BAD_ALGO: return "unknown algorithm";
+    case B200S_ERR_BAD_DEPTH: return "depth out of range (0..2, or -1 for the tuner table)";
+    case B200S_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case B200S_ERR_CUDA: return "CUDA call failed";
+    case B200S_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
+    case B200S_ERR_DEVICE_TIMEOUT: return "a kernel gave up on a bounded wait";
+    case B200S_ERR_TUNER_IO: return "tuner table file could not be read or written";
+    case B200S_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+  }
+  return "unknown status";
+}
+
+const char* b200s_last_cuda_error(void) { return g_cuda_error; }
+
+int64_t b200s_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200s_resolve(const b200s_problem* p, int32_t* algo_out, int32_t* depth_out) {
+  if (!p || !algo_out || !depth_out) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  *algo_out = plan.algo;
+  *depth_out = plan.depth;
+  return B200S_OK;
+}
+
+int b200s_workspace_bytes(const b200s_problem* p, size_t* bytes_out) {
+  if (!p || !bytes_out) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  *bytes_out = plan.total_bytes;
+  return B200S_OK;
+}
+
+int b200s_preadd(const b200s_problem* p, int side, const void* X, void* out, void* stream) {
+  if (!p || !X || !out) return B200S_ERR_NULL_POINTER;
+  if (side != 0 && side != 1) return B200S_ERR_BAD_SHAPE;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  if (plan.depth == 0) return B200S_ERR_BAD_DEPTH;
+  PreaddArgs a;
+  a.X = X;
+  a.out = out;
+  a.batch = p->batch;
+  a.side = side;
+  a.algo = plan.algo;
+  a.depth = plan.depth;
+  a.dtype = p->in_dtype;
+  if (side == 0) {
+    const bool kmaj = p->a_major == B200S_K_MAJOR;
+    a.rows_blk = kmaj ? plan.Mb : plan.Kb;
+    a.cols_blk = kmaj ? plan.Kb : plan.Mb;
+    a.ld = p->lda;
+    a.strideX = p->strideA;
+    a.transposed = !kmaj;
+  } else {
+    const bool kmaj = p->b_major == B200S_K_MAJOR;
+    a.rows_blk = kmaj ? plan.Nb : plan.Kb;
+    a.cols_blk = kmaj ? plan.Kb : plan.Nb;
+    a.ld = p->ldb;
+    a.strideX = p->strideB;
+    a.transposed = kmaj;
+  }
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  return launch_preadd(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200s_combine(const b200s_problem* p, const void* products, void* C, void* stream) {
+  if (!p || !products || !C) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  if (plan.depth == 0) return B200S_ERR_BAD_DEPTH;
+  CombineArgs c;
+  c.products = products;
+  c.C = C;
+  c.Mb = plan.Mb;
+  c.Nb = plan.Nb;
+  c.ldc = p->ldc;
+  c.batch = p->batch;
+  c.strideC = p->strideC;
+  c.algo = plan.algo;
+  c.depth = plan.depth;
+  c.prod_dtype = plan.prod_dtype;
+  c.out_dtype = p->out_dtype;
+  c.beta = p->beta;
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  return launch_combine(c, static_cast<cudaStream_t>(stream));
+}
+
+int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, void* workspace,
+                 size_t workspace_bytes, void* stream_v) {
+  if (!p || !A || !B || !C) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  if (plan.total_bytes > 0) {
+    if (!workspace) return B200S_ERR_NULL_POINTER;
+    if (workspace_bytes < plan.total_bytes) return B200S_ERR_WORKSPACE_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return B200S_ERR_BAD_ALIGNMENT;
+  }
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  GemmArgs g;
+  g.cta_group = p->tile_variant;
+  if (g.cta_group < 0 || g.cta_group > 2) return B200S_ERR_BAD_SHAPE;
+  g.in_dtype = p->in_dtype;
+  g.a_major = p->a_major;
+  g.b_major = p->b_major;
+  if (plan.depth == 0) {
+    g.A = A, g.B = B, g.C = C;
+    g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
+    g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
+    g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
+    g.out_dtype = p->out_dtype;
+    g.beta = p->beta;
+    return launch_gemm(g, stream);
+  }
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* Sa = ws;
+  void* Sb = ws + plan.sa_bytes;
+  void* Mp = ws + plan.sa_bytes + plan.sb_bytes;
+
+  rc = b200s_preadd(p, 0, A, Sa, stream_v);
+  if (rc) return rc;
+  rc = b200s_preadd(p, 1, B, Sb, stream_v);
+  if (rc) return rc;
+
+  const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+  g.A = Sa, g.B = Sb, g.C = Mp;
+  g.M = plan.Mb, g.N = plan.Nb, g.K = plan.Kb;
+  g.batch = p->batch * plan.np;
+  g.lda = a_k ? plan.Kb : plan.Mb;
+  g.ldb = b_k ? plan.Kb : plan.Nb;
+  g.ldc = plan.Nb;
+  g.strideA = plan.Mb * plan.Kb;
+  g.strideB = plan.Kb * plan.Nb;
+  g.strideC = plan.Mb * plan.Nb;
+  g.out_dtype = plan.prod_dtype;
+  g.beta = 0;
+  rc = launch_gemm(g, stream);
+  if (rc) return rc;
+
+  return b200s_combine(p, Mp, C, stream_v);
+}
+
+int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out) {
+  if (!status_out) return B200S_ERR_NULL_POINTER;
+  uint32_t* words = device_status_words();
+  if (!words) return B200S_ERR_NO_DEVICE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t host[2] = {0, 0};
+  B200S_CUDA_OK(cudaMemcpyAsync(host, words, sizeof(host), cudaMemcpyDeviceToHost, s));
+  B200S_CUDA_OK(cudaStreamSynchronize(s));
+  if (host[0] != 0) {
+    B200S_CUDA_OK(cudaMemsetAsync(words, 0, sizeof(host), s));
+    B200S_CUDA_OK(cudaStreamSynchronize(s));
+  }
+  *status_out = host[0] ? B200S_ERR_DEVICE_TIMEOUT : B200S_OK;
+  if (detail_out) *detail_out = static_cast<int32_t>(host[1]);
+  return B200S_OK;
+}
+
+// ---- tuner -----------------------------------------------------------------------------------
+
+int b200s_tuner_clear(void) {
+  std::lock_guard<std::mutex> lock(g_tuner_mu);
+  g_tuner.clear();
+  return B200S_OK;
+}
+
+int b200s_tuner_record(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t algo, int32_t depth) {
+  if (M <= 0 || N <= 0 || K <= 0) return B200S_ERR_BAD_SHAPE;
+  if (!valid_dtype(in_dtype)) return B200S_ERR_BAD_DTYPE;
+  if (algo < B200S_ALGO_DENSE || algo > B200S_ALGO_WINOGRAD) return B200S_ERR_BAD_ALGO;
+  if (depth < 0 || depth > 2) return B200S_ERR_BAD_DEPTH;
+  if (algo == B200S_ALGO_DENSE) depth = 0;
+  std::lock_guard<std::mutex> lock(g_tuner_mu);
+  for (auto& e : g_tuner) {
+    if (e.M == M && e.N == N && e.K == K && e.in_dtype == in_dtype) {
+      e.algo = algo, e.depth = depth;
+      return B200S_OK;
+    }
+  }
+  g_tuner.push_back({M, N, K, in_dtype, algo, depth});
+  return B200S_OK;
+}
+
+int b200s_tuner_lookup(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t* algo_out, int32_t* depth_out) {
+  if (!algo_out || !depth_out) return B200S_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0) return B200S_ERR_BAD_SHAPE;
+  std::lock_guard<std::mutex> lock(g_tuner_mu);
+  const TunerEntry* best = nullptr;
+  double best_d = 0;
+  const double lm = std::log2(static_cast<double>(M)), ln = std::log2(static_cast<double>(N)),
+               lk = std::log2(static_cast<double>(K));
+  for (const auto& e : g_tuner) {
+    if (e.in_dtype != in_dtype) continue;
+    const double dm = lm - std::log2(static_cast<double>(e.M)), dn = ln - std::log2(static_cast<double>(e.N)),
+                 dk = lk - std::log2(static_cast<double>(e.K));
+    const double d = dm * dm + dn * dn + dk * dk;
+    if (!best || d < best_d) best = &e, best_d = d;
+  }
+  if (!best) {
+    default_choice(M, N, K, algo_out, depth_out);
+    return B200S_OK;
+  }
+  *algo_out = best->algo;
+  *depth_out = best->depth;
+  return B200S_OK;
+}
+
+int b200s_tuner_load(const char* path) {
+  if (!path) return B200S_ERR_NULL_POINTER;
+  std::FILE* f = std::fopen(path, "r");
+  if (!f) return B200S_ERR_TUNER_IO;
+  std::vector<TunerEntry> entries;
+  char line[256];
+  bool bad = false;
+  while (std::fgets(line, sizeof(line), f)) {
+    if (line[0] == '#' || line[0] == '\n' || line[0] == '\0') continue;
+    long long m, n, k;
+    int dt, algo, depth;
+    if (std::sscanf(line, "%lld %lld %lld %d %d %d", &m, &n, &k, &dt, &algo, &depth) != 6 || m <= 0 || n <= 0 ||
+        k <= 0 || !valid_dtype(dt) || algo < B200S_ALGO_DENSE || algo > B200S_ALGO_WINOGRAD || depth < 0 ||
+        depth > 2) {
+      bad = true;
+      break;
+    }
+    entries.push_back({m, n, k, dt, algo, algo == B200S_ALGO_DENSE ? 0 : depth});
+  }
+  std::fclose(f);
+  if (bad) return B200S_ERR_TUNER_IO;  // a corrupt file leaves the current table untouched
+  std::lock_guard<std::mutex> lock(g_tuner_mu);
+  g_tuner.swap(entries);
+  return B200S_OK;
+}
+
+int b200s_tuner_save(const char* path) {
+  if (!path) return B200S_ERR_NULL_POINTER;
+  std::FILE* f = std::fopen(path, "w");
+  if (!f) return B200S_ERR_TUNER_IO;
+  std::lock_guard<std::mutex> lock(g_tuner_mu);
+  std::fprintf(f, "# M N K in_dtype algo depth\n");
+  for (const auto& e : g_tuner)
+    std::fprintf(f, "%lld %lld %lld %d %d %d\n", static_cast<long long>(e.M), static_cast<long long>(e.N),
+                 static_cast<long long>(e.K), e.in_dtype, e.algo, e.depth);
+  std::fclose(f);
+  return B200S_OK;
+}
+
+}  // extern "C"

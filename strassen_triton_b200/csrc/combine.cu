@@ -1,0 +1,234 @@
+// Recombination pass of the Strassen pipeline.
+//
+// Each thread reads one 16-byte position of all 7^depth product blocks, accumulates the
+// 4^depth signed output sums in fp32 registers (all levels at once) and writes, or adds into,
+// the 4^depth blocks of C, rounding once to the output dtype. Every product element is read
+// exactly once and every element of C written exactly once; accesses are 128-bit and coalesced.
+//
+// It carries the post-additions and the quadrant assembly of the reference:
+// fixed_strassen_fp32_agg.py:47-56 and :115-123 (products widened to fp32, summed, rounded to
+// base_dtype, vstack/hstack). With beta = 1 it adds into C as the reference's run_* launchers do
+// (strassen.py:184-192).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <utility>
+
+#include "common.h"
+#include "schedule.h"
+
+namespace b200s {
+
+namespace {
+
+struct CombineKernelParams {
+  const void* products;
+  void* C;
+  int64_t Mb, nb_vec;  // block rows, 16-byte product vectors per block row
+  int64_t ldc, strideC;
+  int32_t out_dtype, beta, vec_ok;
+};
+
+template <typename T>
+struct PVec {
+  static constexpr int N = 16 / sizeof(T);
+};
+
+template <typename T>
+__device__ __forceinline__ void load_pvec(const T* ptr, float (&f)[PVec<T>::N]);
+template <>
+__device__ __forceinline__ void load_pvec<float>(const float* ptr, float (&f)[4]) {
+  const float4 v = __ldcs(reinterpret_cast<const float4*>(ptr));
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_pvec<__nv_bfloat16>(const __nv_bfloat16* ptr, float (&f)[8]) {
+  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(ptr));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load_pvec<__half>(const __half* ptr, float (&f)[8]) {
+  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(ptr));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT cvt(float v);
+template <>
+__device__ __forceinline__ float cvt<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half cvt<__half>(float v) {
+  return __float2half_rn(v);
+}
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+
+// Writes N consecutive output elements, as 16-byte vectors when aligned.
+template <typename OutT, int N>
+__device__ __forceinline__ void store_out(OutT* dst, const float (&f)[N], bool beta, bool vec_ok) {
+  constexpr int kPer = 16 / sizeof(OutT);
+  if constexpr (N >= kPer) {
+    if (vec_ok) {
+#pragma unroll
+      for (int v = 0; v < N / kPer; ++v) {
+        union {
+          uint4 u;
+          OutT e[kPer];
+        } pack;
+        if (beta) {
+          pack.u = *reinterpret_cast<const uint4*>(dst + v * kPer);
+#pragma unroll
+          for (int i = 0; i < kPer; ++i) pack.e[i] = cvt<OutT>(widen(pack.e[i]) + f[v * kPer + i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < kPer; ++i) pack.e[i] = cvt<OutT>(f[v * kPer + i]);
+        }
+        *reinterpret_cast<uint4*>(dst + v * kPer) = pack.u;
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) dst[i] = cvt<OutT>(beta ? widen(dst[i]) + f[i] : f[i]);
+}
+
+template <int DEPTH, int ALGO, typename TP>
+struct Combine {
+  static constexpr int NQ = sched::ipow(4, DEPTH);
+  static constexpr int NP = sched::ipow(7, DEPTH);
+  static constexpr int VEC = PVec<TP>::N;
+
+  template <int P, int R>
+  static __device__ __forceinline__ void add_term(const float (&x)[VEC], float (&acc)[NQ][VEC]) {
+    constexpr int c = sched::w(ALGO, DEPTH, R, P);
+    if constexpr (c != 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[R][i] = c > 0 ? acc[R][i] + x[i] : acc[R][i] - x[i];
+    }
+  }
+
+  template <int P, int... Rs>
+  static __device__ __forceinline__ void one_product(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
+                                                     std::integer_sequence<int, Rs...>) {
+    float x[VEC];
+    load_pvec<TP>(prod0 + P * blk_elems, x);
+    (add_term<P, Rs>(x, acc), ...);
+  }
+
+  template <int... Ps>
+  static __device__ __forceinline__ void all_products(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
+                                                      std::integer_sequence<int, Ps...>) {
+    (one_product<Ps>(prod0, blk_elems, acc, std::make_integer_sequence<int, NQ>{}), ...);
+  }
+};
+
+template <int DEPTH, int ALGO, typename TP>
+__global__ void __launch_bounds__(256) combine_kernel(const CombineKernelParams p) {
+  using CB = Combine<DEPTH, ALGO, TP>;
+  constexpr int NQ = CB::NQ, NP = CB::NP, VEC = CB::VEC;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.Mb * p.nb_vec) return;
+  const int64_t row = idx / p.nb_vec;
+  const int64_t cv = idx - row * p.nb_vec;
+  const int64_t Nb = p.nb_vec * VEC;
+  const int64_t blk_elems = p.Mb * Nb;
+
+  float acc[NQ][VEC];
+#pragma unroll
+  for (int r = 0; r < NQ; ++r)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[r][i] = 0.f;
+
+  const TP* prod0 =
+      static_cast<const TP*>(p.products) + static_cast<int64_t>(blockIdx.y) * NP * blk_elems + row * Nb + cv * VEC;
+  CB::all_products(prod0, blk_elems, acc, std::make_integer_sequence<int, NP>{});
+
+#pragma unroll
+  for (int r = 0; r < NQ; ++r) {
+    const int64_t crow = sched::block_row(DEPTH, r) * p.Mb + row;
+    const int64_t ccol = sched::block_col(DEPTH, r) * Nb + cv * VEC;
+    const int64_t off = static_cast<int64_t>(blockIdx.y) * p.strideC + crow * p.ldc + ccol;
+    if (p.out_dtype == B200S_BF16)
+      store_out<__nv_bfloat16, VEC>(static_cast<__nv_bfloat16*>(p.C) + off, acc[r], p.beta != 0, p.vec_ok != 0);
+    else if (p.out_dtype == B200S_FP16)
+      store_out<__half, VEC>(static_cast<__half*>(p.C) + off, acc[r], p.beta != 0, p.vec_ok != 0);
+    else
+      store_out<float, VEC>(static_cast<float*>(p.C) + off, acc[r], p.beta != 0, p.vec_ok != 0);
+  }
+}
+
+template <int DEPTH, int ALGO, typename TP>
+int launch_one(const CombineArgs& a, cudaStream_t stream) {
+  constexpr int VEC = PVec<TP>::N;
+  CombineKernelParams kp;
+  kp.products = a.products;
+  kp.C = a.C;
+  kp.Mb = a.Mb;
+  kp.nb_vec = a.Nb / VEC;
+  kp.ldc = a.ldc;
+  kp.strideC = a.strideC;
+  kp.out_dtype = a.out_dtype;
+  kp.beta = a.beta;
+  const size_t oes = dtype_size(a.out_dtype);
+  kp.vec_ok = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) && ((a.ldc * oes) % 16 == 0) &&
+              ((a.Nb * oes) % 16 == 0) && (a.batch == 1 || (a.strideC * oes) % 16 == 0);
+  const int64_t total = kp.Mb * kp.nb_vec;
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.batch));
+  combine_kernel<DEPTH, ALGO, TP><<<grid, 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
+
+template <int DEPTH, int ALGO>
+int launch_dtype(const CombineArgs& a, cudaStream_t stream) {
+  switch (a.prod_dtype) {
+    case B200S_BF16:
+      return launch_one<DEPTH, ALGO, __nv_bfloat16>(a, stream);
+    case B200S_FP16:
+      return launch_one<DEPTH, ALGO, __half>(a, stream);
+    case B200S_FP32:
+      return launch_one<DEPTH, ALGO, float>(a, stream);
+  }
+  return B200S_ERR_BAD_DTYPE;
+}
+
+}  // namespace
+
+int launch_combine(const CombineArgs& a, cudaStream_t stream) {
+  const size_t pes = dtype_size(a.prod_dtype);
+  const int vec = static_cast<int>(16 / pes);
+  if (a.Mb <= 0 || a.Nb <= 0 || a.batch <= 0) return B200S_ERR_BAD_SHAPE;
+  if (a.Nb % vec) return B200S_ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(a.products) & 15u) return B200S_ERR_BAD_ALIGNMENT;
+  const bool wino = a.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && a.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (a.depth == 1)
+    return wino ? launch_dtype<1, sched::kWinograd>(a, stream) : launch_dtype<1, sched::kClassic>(a, stream);
+  if (a.depth == 2)
+    return wino ? launch_dtype<2, sched::kWinograd>(a, stream) : launch_dtype<2, sched::kClassic>(a, stream);
+  return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s

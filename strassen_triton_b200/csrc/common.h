@@ -1,0 +1,69 @@
+// Internal declarations shared by the translation units of libb200s.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b200s.h"
+
+namespace b200s {
+
+// ---- host-side bookkeeping (api.cu) -------------------------------------------------------
+void note_cuda_error(cudaError_t e, const char* where);
+void count_launch(int n = 1);
+// Device status words (2 x uint32) of the current device, allocated on first use. nullptr on failure.
+uint32_t* device_status_words();
+int sm_count();
+
+#define B200S_CUDA_OK(expr)                          \
+  do {                                               \
+    cudaError_t e__ = (expr);                        \
+    if (e__ != cudaSuccess) {                        \
+      ::b200s::note_cuda_error(e__, #expr);          \
+      return B200S_ERR_CUDA;                         \
+    }                                                \
+  } while (0)
+
+inline size_t dtype_size(int dt) { return dt == B200S_FP32 ? 4 : 2; }
+
+// ---- GEMM (gemm_sm100.cu) -----------------------------------------------------------------
+// C[b] (+)= A[b] . B[b] for b < batch; all operands on the device. Leading dimensions and
+// batch strides in elements. in_dtype fp32 runs as TF32.
+struct GemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  int64_t M, N, K, batch;
+  int64_t lda, ldb, ldc;
+  int64_t strideA, strideB, strideC;
+  int a_major, b_major;
+  int in_dtype, out_dtype;
+  int beta;
+  int cta_group;  // 0 = default, 1 or 2 = force
+};
+int launch_gemm(const GemmArgs& g, cudaStream_t stream);
+
+// ---- Strassen schedule (schedule.h) and its passes (preadd.cu, combine.cu) ----------------
+struct PreaddArgs {
+  const void* X;   // one operand, storage rows x cols with the contiguous dimension last
+  void* out;       // 7^depth blocks, block p at out + p * rows_blk * cols_blk
+  int64_t rows_blk, cols_blk;  // extents of one block in storage orientation
+  int64_t ld;                  // elements between storage rows of X
+  int64_t batch, strideX;      // batch stride of X in elements; output batch stride is 7^depth blocks
+  int transposed;  // storage rows run along the logical column index of the operand
+  int side;        // 0 = A (table U), 1 = B (table V)
+  int algo, depth, dtype;
+};
+int launch_preadd(const PreaddArgs& a, cudaStream_t stream);
+
+struct CombineArgs {
+  const void* products;  // 7^depth blocks of Mb x Nb, row-major, block p at p * Mb * Nb
+  void* C;
+  int64_t Mb, Nb, ldc;
+  int64_t batch, strideC;
+  int algo, depth, prod_dtype, out_dtype, beta;
+};
+int launch_combine(const CombineArgs& a, cudaStream_t stream);
+
+}  // namespace b200s

@@ -1,0 +1,538 @@
+// Batched / grouped dense GEMM for sm_100a: C[b] (+)= A[b] . B[b].
+//
+// One persistent, warp-specialised kernel:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128-byte-swizzled operand tiles
+//               into a ring of shared-memory stages
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (fp32 accumulators in TMEM)
+//   warps 2..5  epilogue: tcgen05.ld of a finished accumulator, conversion, stores to C
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop
+// of tile i+1. With kCtaGroup == 2 two CTAs of a cluster share one 256-row tile
+// (tcgen05.mma.cta_group::2): each CTA loads its own 128 rows of A and its half of the B tile,
+// the leader CTA issues the MMAs for both.
+//
+// The 7 or 49 sub-products of a Strassen step are one launch of this kernel: the batch
+// coordinate of the 3-D tensor maps selects the product, tiles are ordered product-major so one
+// product's operands stay in L2 while its tiles run.
+//
+// It stands where the reference calls torch.mm (cuBLAS) for its sub-products:
+// fixed_strassen_fp32_agg.py:38-44, fixed_strassen.py:39-45, strassen.py:722-728, and where it
+// launches its dense Triton kernel, strassen.py:31-88.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace b200s {
+
+namespace {
+
+constexpr int kBM = 128;          // accumulator rows per CTA (TMEM lanes)
+constexpr int kRowBytes = 128;    // bytes of one swizzled smem row = one K block of a K-major tile
+constexpr int kThreads = 192;
+
+struct GemmKernelParams {
+  int32_t M, N;               // extents of one C[b]
+  int32_t m_tiles, n_tiles;   // tiles per batch item
+  int32_t k_blocks;
+  int32_t total_tiles;
+  int32_t a_mn, b_mn;
+  int32_t fmt;                // operand format field of the instruction descriptor
+  int32_t out_dtype, beta;
+  int64_t ldc, strideC;
+  void* C;
+  uint32_t* status;
+};
+
+// Role codes stored in the abort word / device status when a wait runs out.
+enum : uint32_t { kWhoProducer = 1, kWhoMma = 2, kWhoMmaAcc = 3, kWhoEpilogue = 4 };
+
+__device__ __forceinline__ void decode_tile(const GemmKernelParams& p, int tile, int& b, int& mt,
+                                            int& nt) {
+  constexpr int kGroup = 8;  // m-tiles per L2 group
+  const int per_batch = p.m_tiles * p.n_tiles;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  const int per_group = kGroup * p.n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * kGroup;
+  const int gsz = min(kGroup, p.m_tiles - first_m);
+  t -= g * per_group;
+  mt = first_m + t % gsz;
+  nt = t / gsz;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT cvt_out(float v);
+template <>
+__device__ __forceinline__ float cvt_out<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half cvt_out<__half>(float v) {
+  return __float2half_rn(v);
+}
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+// Writes 32 consecutive columns of one row. `ncols` (<= 32) of them are inside the matrix.
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], int ncols,
+                                            bool vec_ok, bool beta) {
+  constexpr int kPerVec = 16 / sizeof(OutT);
+  if (vec_ok && ncols == 32) {
+#pragma unroll
+    for (int v = 0; v < 32 / kPerVec; ++v) {
+      union {
+        uint4 u;
+        OutT e[kPerVec];
+      } pack;
+      if (beta) {
+        pack.u = *reinterpret_cast<const uint4*>(dst + v * kPerVec);
+#pragma unroll
+        for (int i = 0; i < kPerVec; ++i)
+          pack.e[i] = cvt_out<OutT>(to_f32(pack.e[i]) + __uint_as_float(r[v * kPerVec + i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < kPerVec; ++i) pack.e[i] = cvt_out<OutT>(__uint_as_float(r[v * kPerVec + i]));
+      }
+      *reinterpret_cast<uint4*>(dst + v * kPerVec) = pack.u;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i < ncols) {
+        float v = __uint_as_float(r[i]);
+        if (beta) v += to_f32(dst[i]);
+        dst[i] = cvt_out<OutT>(v);
+      }
+    }
+  }
+}
+
+template <int kCtaGroup, int BN, int kStages, bool kTf32>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmKernelParams p) {
+  constexpr int ES = kTf32 ? 4 : 2;              // operand element size
+  constexpr int BKE = kRowBytes / ES;            // K elements per stage
+  constexpr int BN_CTA = BN / kCtaGroup;         // B-tile rows this CTA loads
+  constexpr int A_BYTES = kBM * kRowBytes;
+  constexpr int B_BYTES = BN_CTA * kRowBytes;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int CHUNK_E = kRowBytes / ES;        // MN elements per 128-byte row of an MN-major tile
+  constexpr int CHUNK_BYTES = BKE * kRowBytes;   // one MN-major chunk: BKE k-rows of 128 bytes
+  constexpr int UMMA_K = 32 / ES;                // K elements per tcgen05.mma
+  constexpr int K_STEPS = BKE / UMMA_K;          // = 4
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+
+  // Barrier block lives after the stages.
+  const uint32_t bar_base = base + kStages * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(gbase + kStages * STAGE_BYTES + 8 * (2 * kStages + 4));
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / kCtaGroup;
+  const int num_clusters = gridDim.x / kCtaGroup;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar(b), 1);
+      ptx::mbar_init(tempty_bar(b), 4 * kCtaGroup);
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<kCtaGroup>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    ptx::tmem_relinquish<kCtaGroup>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool alive = true;
+      for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters) {
+        int b, mt, nt;
+        decode_tile(p, tile, b, mt, nt);
+        const int m0 = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM;
+        const int n0 = nt * BN + static_cast<int>(cta_rank) * BN_CTA;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!ptx::mbar_wait<kCtaGroup == 2>(empty_bar(stage), phase ^ 1u, abort_word, kWhoProducer)) {
+            alive = false;
+            break;
+          }
+          const uint32_t sA = base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + A_BYTES;
+          const int k0 = kb * BKE;
+          if constexpr (kCtaGroup == 1) {
+            const uint32_t fb = full_bar(stage);
+            ptx::mbar_expect_tx(fb, STAGE_BYTES);
+            if (!p.a_mn) {
+              ptx::tma_load_3d(sA, &tmA, fb, k0, m0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kBM / CHUNK_E; ++j)
+                ptx::tma_load_3d(sA + j * CHUNK_BYTES, &tmA, fb, m0 + j * CHUNK_E, k0, b);
+            }
+            if (!p.b_mn) {
+              ptx::tma_load_3d(sB, &tmB, fb, k0, n0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / CHUNK_E; ++j)
+                ptx::tma_load_3d(sB + j * CHUNK_BYTES, &tmB, fb, n0 + j * CHUNK_E, k0, b);
+            }
+          } else {
+            // Both CTAs' bytes are counted on the leader's barrier.
+            const uint32_t fb = ptx::mapa_cluster(full_bar(stage), 0);
+            if (cta_rank == 0) ptx::mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+            if (!p.a_mn) {
+              ptx::tma_load_3d_pair(sA, &tmA, fb, k0, m0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kBM / CHUNK_E; ++j)
+                ptx::tma_load_3d_pair(sA + j * CHUNK_BYTES, &tmA, fb, m0 + j * CHUNK_E, k0, b);
+            }
+            if (!p.b_mn) {
+              ptx::tma_load_3d_pair(sB, &tmB, fb, k0, n0, b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / CHUNK_E; ++j)
+                ptx::tma_load_3d_pair(sB + j * CHUNK_BYTES, &tmB, fb, n0 + j * CHUNK_E, k0, b);
+            }
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = ptx::make_instr_desc(static_cast<uint32_t>(p.fmt), p.a_mn, p.b_mn, kBM * kCtaGroup, BN);
+      // K-major: 8-row groups 1024 bytes apart, K advances 32 bytes inside the swizzled row.
+      // MN-major: 8-k-row groups 1024 bytes apart (SBO), 128-byte MN chunks CHUNK_BYTES apart (LBO).
+      const uint32_t a_lbo = p.a_mn ? CHUNK_BYTES : 16u, b_lbo = p.b_mn ? CHUNK_BYTES : 16u;
+      const uint32_t a_adv = p.a_mn ? (UMMA_K / 8) * 1024u : 32u;
+      const uint32_t b_adv = p.b_mn ? (UMMA_K / 8) * 1024u : 32u;
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool alive = true;
+      for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters, ++it) {
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1u;
+        if (!ptx::mbar_wait<kCtaGroup == 2>(tempty_bar(buf), aphase ^ 1u, abort_word, kWhoMmaAcc)) {
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!ptx::mbar_wait<kCtaGroup == 2>(full_bar(stage), phase, abort_word, kWhoMma)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sA = base + stage * STAGE_BYTES;
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < K_STEPS; ++k) {
+            const uint64_t ad = ptx::make_smem_desc(sA + k * a_adv, a_lbo, 1024u);
+            const uint64_t bd = ptx::make_smem_desc(sB + k * b_adv, b_lbo, 1024u);
+            ptx::umma<kCtaGroup, kTf32>(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // Frees the stage (in both CTAs) once the MMAs above have read it.
+          ptx::umma_commit<kCtaGroup>(empty_bar(stage));
+          if constexpr (kCtaGroup == 2) ptx::umma_commit<kCtaGroup>(ptx::mapa_cluster(empty_bar(stage), 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!alive) break;
+        ptx::umma_commit<kCtaGroup>(tfull_bar(buf));
+        if constexpr (kCtaGroup == 2) ptx::umma_commit<kCtaGroup>(ptx::mapa_cluster(tfull_bar(buf), 1));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
+    const int out_dt = p.out_dtype;
+    const size_t out_es = (out_dt == B200S_FP32) ? 4 : 2;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && ((p.ldc * out_es) % 16 == 0) &&
+                        ((p.strideC * out_es) % 16 == 0);
+    int it = 0;
+    for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it) {
+      int b, mt, nt;
+      decode_tile(p, tile, b, mt, nt);
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1u;
+      bool ok = ptx::mbar_wait<kCtaGroup == 2>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const int row = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM + lane_group * 32 + lane;
+      const int col0 = nt * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                             static_cast<uint32_t>(buf * BN);
+      uint8_t* crow = static_cast<uint8_t*>(p.C) +
+                      (static_cast<int64_t>(b) * p.strideC + static_cast<int64_t>(row) * p.ldc) * out_es;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col = col0 + c * 32;
+        const int ncols = min(32, p.N - col);
+        if (row < p.M && ncols > 0) {
+          if (out_dt == B200S_BF16)
+            store_row32(reinterpret_cast<__nv_bfloat16*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+          else if (out_dt == B200S_FP16)
+            store_row32(reinterpret_cast<__half*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+          else
+            store_row32(reinterpret_cast<float*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCtaGroup == 2)
+          ptx::mbar_arrive_cluster(tempty_bar(buf), 0);
+        else
+          ptx::mbar_arrive(tempty_bar(buf));
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    // Neither CTA may leave while its peer can still signal its barriers or read its tiles.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (threadIdx.x == 0 && *abort_word != 0) {
+    atomicExch(&p.status[0], 1u);
+    atomicExch(&p.status[1], *abort_word);
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<kCtaGroup>(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+// Tensor map over an operand stored as [batch][rows][cols], cols contiguous, with a box of
+// box_rows x (128 bytes of cols) and the 128-byte swizzle.
+int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int64_t ld,
+                     int64_t batch, int64_t batch_stride, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200S_ERR_CUDA;
+  const size_t es = dtype_size(dtype);
+  CUtensorMapDataType dt = dtype == B200S_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype == B200S_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(batch)};
+  // A single batch item still needs a legal (multiple of 16 bytes) outer stride.
+  int64_t bs = batch > 1 ? batch_stride : rows * ld;
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es, static_cast<cuuint64_t>(bs) * es};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / es), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return B200S_ERR_CUDA;
+  }
+  return B200S_OK;
+}
+
+template <int kCtaGroup, int BN, int kStages, bool kTf32>
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmKernelParams kp, cudaStream_t stream) {
+  constexpr int BN_CTA = BN / kCtaGroup;
+  constexpr int STAGE_BYTES = kBM * kRowBytes + BN_CTA * kRowBytes;
+  constexpr int SMEM = kStages * STAGE_BYTES + 8 * (2 * kStages + 4) + 16 + 1024;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+  auto kernel = gemm_kernel<kCtaGroup, BN, kStages, kTf32>;
+
+  // Per-device one-time setup: opt in to the shared-memory size and find out how many
+  // clusters can be resident at once (static tile striding needs all of them co-resident).
+  static std::mutex mu;
+  static int max_clusters[64] = {0};
+  int dev = 0;
+  B200S_CUDA_OK(cudaGetDevice(&dev));
+  int resident;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) return B200S_ERR_NO_DEVICE;
+    if (max_clusters[dev] == 0) {
+      B200S_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+      int n = sm_count() / kCtaGroup;
+      if (kCtaGroup == 2) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sm_count() / 2 * 2);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = SMEM;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int q = 0;
+        B200S_CUDA_OK(cudaOccupancyMaxActiveClusters(&q, kernel, &cfg));
+        if (q < 1) return B200S_ERR_CUDA;
+        if (q < n) n = q;
+      }
+      max_clusters[dev] = n;
+    }
+    resident = max_clusters[dev];
+  }
+
+  const int clusters = kp.total_tiles < resident ? kp.total_tiles : resident;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * kCtaGroup);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = kCtaGroup;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  B200S_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, kp));
+  count_launch();
+  return B200S_OK;
+}
+
+}  // namespace
+
+int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) return B200S_ERR_BAD_SHAPE;
+  if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return B200S_ERR_BAD_SHAPE;
+  const bool tf32 = g.in_dtype == B200S_FP32;
+  const size_t es = dtype_size(g.in_dtype);
+  if ((reinterpret_cast<uintptr_t>(g.A) & 15u) || (reinterpret_cast<uintptr_t>(g.B) & 15u))
+    return B200S_ERR_BAD_ALIGNMENT;
+  if ((g.lda * es) % 16 || (g.ldb * es) % 16) return B200S_ERR_BAD_STRIDE;
+  if (g.batch > 1 && ((g.strideA * es) % 16 || (g.strideB * es) % 16)) return B200S_ERR_BAD_STRIDE;
+
+  uint32_t* status = device_status_words();
+  if (!status) return B200S_ERR_CUDA;
+
+  int cta_group = g.cta_group;
+  if (cta_group == 0) cta_group = 2;
+  const int BN = 256;
+  const int bke = kRowBytes / static_cast<int>(es);
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  // K-major operands are stored [rows = M or N][cols = K]; MN-major ones [rows = K][cols = M or N].
+  if (g.a_major == B200S_K_MAJOR)
+    rc = make_operand_map(&tmA, g.A, g.in_dtype, g.M, g.K, g.lda, g.batch, g.strideA, kBM);
+  else
+    rc = make_operand_map(&tmA, g.A, g.in_dtype, g.K, g.M, g.lda, g.batch, g.strideA, bke);
+  if (rc) return rc;
+  const int bn_cta = BN / cta_group;
+  if (g.b_major == B200S_K_MAJOR)
+    rc = make_operand_map(&tmB, g.B, g.in_dtype, g.N, g.K, g.ldb, g.batch, g.strideB, bn_cta);
+  else
+    rc = make_operand_map(&tmB, g.B, g.in_dtype, g.K, g.N, g.ldb, g.batch, g.strideB, bke);
+  if (rc) return rc;
+
+  GemmKernelParams kp;
+  kp.M = static_cast<int32_t>(g.M);
+  kp.N = static_cast<int32_t>(g.N);
+  const int tile_m = kBM * cta_group;
+  kp.m_tiles = static_cast<int32_t>((g.M + tile_m - 1) / tile_m);
+  kp.n_tiles = static_cast<int32_t>((g.N + BN - 1) / BN);
+  kp.k_blocks = static_cast<int32_t>((g.K + bke - 1) / bke);
+  const int64_t total = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles * g.batch;
+  if (total > INT32_MAX) return B200S_ERR_BAD_SHAPE;
+  kp.total_tiles = static_cast<int32_t>(total);
+  kp.a_mn = g.a_major == B200S_MN_MAJOR;
+  kp.b_mn = g.b_major == B200S_MN_MAJOR;
+  kp.fmt = tf32 ? 2 : (g.in_dtype == B200S_BF16 ? 1 : 0);
+  kp.out_dtype = g.out_dtype;
+  kp.beta = g.beta;
+  kp.ldc = g.ldc;
+  kp.strideC = g.strideC;
+  kp.C = g.C;
+  kp.status = status;
+
+  if (cta_group == 2) {
+    if (tf32) return launch_variant<2, 256, 6, true>(tmA, tmB, kp, stream);
+    return launch_variant<2, 256, 6, false>(tmA, tmB, kp, stream);
+  }
+  if (tf32) return launch_variant<1, 256, 4, true>(tmA, tmB, kp, stream);
+  return launch_variant<1, 256, 4, false>(tmA, tmB, kp, stream);
+}
+
+}  // namespace b200s

@@ -1,0 +1,215 @@
+// Operand pre-addition pass of the Strassen pipeline.
+//
+// One pass over an operand: each thread loads the 4^depth quadrant values at one 16-byte
+// position, forms all 7^depth signed sums in fp32 and writes them, rounded once to the operand
+// dtype, as 7^depth dense blocks that the grouped GEMM reads as its batch. The operand is read
+// exactly once; reads and writes are 128-bit and coalesced along the contiguous dimension.
+//
+// It carries the additions the reference makes before its products:
+// fixed_strassen_fp32_agg.py:26-44 (one level, quadrants widened to fp32, sums rounded to
+// base_dtype) and :77-96 (S1..S10 of the outer level); at two levels the reference rounds S1..S10
+// before forming the inner sums, here both levels are summed in fp32 and rounded once.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <utility>
+
+#include "common.h"
+#include "schedule.h"
+
+namespace b200s {
+
+namespace {
+
+struct PreaddKernelParams {
+  const void* X;
+  void* out;
+  int64_t rows_blk, cols_vec;  // block rows, 16-byte vectors per block row
+  int64_t ld;                  // elements
+  int64_t strideX;             // elements
+  int32_t transposed;
+};
+
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+};
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* ptr, float (&f)[Vec16<T>::N]);
+template <>
+__device__ __forceinline__ void load_vec<float>(const float* ptr, float (&f)[4]) {
+  const float4 v = __ldg(reinterpret_cast<const float4*>(ptr));
+  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* ptr, float (&f)[8]) {
+  const uint4 v = __ldg(reinterpret_cast<const uint4*>(ptr));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load_vec<__half>(const __half* ptr, float (&f)[8]) {
+  const uint4 v = __ldg(reinterpret_cast<const uint4*>(ptr));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T* ptr, const float (&f)[Vec16<T>::N]);
+template <>
+__device__ __forceinline__ void store_vec<float>(float* ptr, const float (&f)[4]) {
+  *reinterpret_cast<float4*>(ptr) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <>
+__device__ __forceinline__ void store_vec<__nv_bfloat16>(__nv_bfloat16* ptr, const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&t);
+  }
+  *reinterpret_cast<uint4*>(ptr) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ __forceinline__ void store_vec<__half>(__half* ptr, const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&t);
+  }
+  *reinterpret_cast<uint4*>(ptr) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <int DEPTH, int ALGO, int SIDE, typename T>
+struct Preadd {
+  static constexpr int NQ = sched::ipow(4, DEPTH);
+  static constexpr int NP = sched::ipow(7, DEPTH);
+  static constexpr int VEC = Vec16<T>::N;
+
+  template <int P, int Q>
+  static __device__ __forceinline__ void add_term(const float (&x)[NQ][VEC], float (&acc)[VEC], bool& first) {
+    constexpr int c = sched::uv(ALGO, SIDE, DEPTH, P, Q);
+    if constexpr (c != 0) {
+      if (first) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = c > 0 ? x[Q][i] : -x[Q][i];
+        first = false;
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = c > 0 ? acc[i] + x[Q][i] : acc[i] - x[Q][i];
+      }
+    }
+  }
+
+  template <int P, int... Qs>
+  static __device__ __forceinline__ void one_product(const float (&x)[NQ][VEC], T* out_blk0, int64_t blk_elems,
+                                                     std::integer_sequence<int, Qs...>) {
+    float acc[VEC];
+    bool first = true;
+    (add_term<P, Qs>(x, acc, first), ...);
+    store_vec<T>(out_blk0 + P * blk_elems, acc);
+  }
+
+  template <int... Ps>
+  static __device__ __forceinline__ void all_products(const float (&x)[NQ][VEC], T* out_blk0, int64_t blk_elems,
+                                                      std::integer_sequence<int, Ps...>) {
+    (one_product<Ps>(x, out_blk0, blk_elems, std::make_integer_sequence<int, NQ>{}), ...);
+  }
+};
+
+template <int DEPTH, int ALGO, int SIDE, typename T>
+__global__ void __launch_bounds__(256) preadd_kernel(const PreaddKernelParams p) {
+  using PA = Preadd<DEPTH, ALGO, SIDE, T>;
+  constexpr int NQ = PA::NQ, NP = PA::NP, VEC = PA::VEC;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.rows_blk * p.cols_vec) return;
+  const int64_t row = idx / p.cols_vec;
+  const int64_t cv = idx - row * p.cols_vec;
+  const int64_t cols_blk = p.cols_vec * VEC;
+  const T* X = static_cast<const T*>(p.X) + static_cast<int64_t>(blockIdx.y) * p.strideX;
+
+  float x[NQ][VEC];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const int lr = sched::block_row(DEPTH, q), lc = sched::block_col(DEPTH, q);
+    const int sr = p.transposed ? lc : lr;
+    const int sc = p.transposed ? lr : lc;
+    load_vec<T>(X + (sr * p.rows_blk + row) * p.ld + sc * cols_blk + cv * VEC, x[q]);
+  }
+  const int64_t blk_elems = p.rows_blk * cols_blk;
+  T* out = static_cast<T*>(p.out) + static_cast<int64_t>(blockIdx.y) * NP * blk_elems + row * cols_blk + cv * VEC;
+  PA::all_products(x, out, blk_elems, std::make_integer_sequence<int, NP>{});
+}
+
+template <int DEPTH, int ALGO, int SIDE, typename T>
+int launch_one(const PreaddArgs& a, cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  PreaddKernelParams kp;
+  kp.X = a.X;
+  kp.out = a.out;
+  kp.rows_blk = a.rows_blk;
+  kp.cols_vec = a.cols_blk / VEC;
+  kp.ld = a.ld;
+  kp.strideX = a.strideX;
+  kp.transposed = a.transposed;
+  const int64_t total = kp.rows_blk * kp.cols_vec;
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.batch));
+  preadd_kernel<DEPTH, ALGO, SIDE, T><<<grid, 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
+
+template <int DEPTH, int ALGO, int SIDE>
+int launch_dtype(const PreaddArgs& a, cudaStream_t stream) {
+  switch (a.dtype) {
+    case B200S_BF16:
+      return launch_one<DEPTH, ALGO, SIDE, __nv_bfloat16>(a, stream);
+    case B200S_FP16:
+      return launch_one<DEPTH, ALGO, SIDE, __half>(a, stream);
+    case B200S_FP32:
+      return launch_one<DEPTH, ALGO, SIDE, float>(a, stream);
+  }
+  return B200S_ERR_BAD_DTYPE;
+}
+
+template <int DEPTH, int ALGO>
+int launch_side(const PreaddArgs& a, cudaStream_t stream) {
+  return a.side == 0 ? launch_dtype<DEPTH, ALGO, sched::kSideA>(a, stream)
+                     : launch_dtype<DEPTH, ALGO, sched::kSideB>(a, stream);
+}
+
+}  // namespace
+
+int launch_preadd(const PreaddArgs& a, cudaStream_t stream) {
+  const size_t es = dtype_size(a.dtype);
+  const int vec = static_cast<int>(16 / es);
+  if (a.rows_blk <= 0 || a.cols_blk <= 0 || a.batch <= 0) return B200S_ERR_BAD_SHAPE;
+  if (a.cols_blk % vec) return B200S_ERR_BAD_SHAPE;
+  if ((a.ld * es) % 16 || (a.batch > 1 && (a.strideX * es) % 16)) return B200S_ERR_BAD_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(a.X) & 15u) || (reinterpret_cast<uintptr_t>(a.out) & 15u))
+    return B200S_ERR_BAD_ALIGNMENT;
+  const bool wino = a.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && a.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (a.depth == 1)
+    return wino ? launch_side<1, sched::kWinograd>(a, stream) : launch_side<1, sched::kClassic>(a, stream);
+  if (a.depth == 2)
+    return wino ? launch_side<2, sched::kWinograd>(a, stream) : launch_side<2, sched::kClassic>(a, stream);
+  return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s

@@ -1,0 +1,178 @@
+"""Tensor-level entry to libb200s.so: `matmul(A, B, ...)` on CUDA tensors, and the autograd
+function every reference-named module in this repository routes through.
+
+torch is plumbing here (device memory, streams, autograd bookkeeping); all arithmetic runs in
+the CUDA library through its C ABI.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_DTYPE = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float32: _lib.FP32}
+_ALGO = {"auto": _lib.ALGO_AUTO, "dense": _lib.ALGO_DENSE, "classic": _lib.ALGO_CLASSIC,
+         "strassen": _lib.ALGO_CLASSIC, "winograd": _lib.ALGO_WINOGRAD}
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"expected a torch.Tensor, got {type(t).__name__}")
+        if not t.is_cuda:
+            raise RuntimeError("b200s kernels run on CUDA tensors only; there is no CPU path "
+                               f"(got a tensor on {t.device})")
+
+
+def _operand(t: torch.Tensor):
+    """(tensor, major_is_inner, ld, batch_stride) for a 2-D or 3-D operand, copying only when
+    neither of the last two dimensions has unit stride or the strides break 16-byte alignment."""
+    es = t.element_size()
+
+    def ok(x):
+        r, c = x.shape[-2], x.shape[-1]
+        sr, sc = x.stride(-2), x.stride(-1)
+        bs = x.stride(0) if x.dim() == 3 else 0
+        if (x.data_ptr() % 16) or (bs * es) % 16:
+            return None
+        if sc == 1 and (sr * es) % 16 == 0 and sr >= c:
+            return (True, sr, bs)       # rows x cols with cols contiguous
+        if sr == 1 and (sc * es) % 16 == 0 and sc >= r:
+            return (False, sc, bs)      # columns contiguous: a transposed view
+        return None
+
+    got = ok(t)
+    if got is None:
+        t = t.contiguous()
+        got = ok(t)
+        if got is None:
+            raise ValueError("operand rows must be a multiple of 16 bytes long "
+                             f"(shape {tuple(t.shape)}, dtype {t.dtype})")
+    return (t,) + got
+
+
+def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precision="tf32",
+                 tile_variant=0):
+    """Fill a ``b200s_problem`` for C (+)= A @ B. Returns (problem, A', B') where A'/B' are the
+    tensors whose pointers must be passed (copies only when the strides force one)."""
+    if A.dim() != B.dim() or A.dim() not in (2, 3):
+        raise ValueError("A and B must both be 2-D, or both 3-D (batched)")
+    if A.dtype != B.dtype or A.dtype not in _DTYPE:
+        raise TypeError(f"unsupported operand dtypes {A.dtype}, {B.dtype}")
+    if C.dtype not in _DTYPE:
+        raise TypeError(f"unsupported output dtype {C.dtype}")
+    M, K = A.shape[-2], A.shape[-1]
+    K2, N = B.shape[-2], B.shape[-1]
+    assert K == K2 and C.shape[-2] == M and C.shape[-1] == N, "shape mismatch"
+    batch = A.shape[0] if A.dim() == 3 else 1
+    if A.dim() == 3:
+        assert B.shape[0] == batch and C.shape[0] == batch, "batch mismatch"
+    if C.stride(-1) != 1:
+        raise ValueError("C must be row-major (unit stride in its last dimension)")
+    A2, a_inner, lda, sa = _operand(A)
+    B2, b_inner, ldb, sb = _operand(B)
+    p = _lib.Problem()
+    p.M, p.N, p.K, p.batch = M, N, K, batch
+    p.lda, p.ldb, p.ldc = lda, ldb, C.stride(-2)
+    p.strideA, p.strideB = sa, sb
+    p.strideC = C.stride(0) if C.dim() == 3 else 0
+    # A is M x K: inner-contiguous means K-major. B is K x N: inner-contiguous means N-major.
+    p.a_major = _lib.K_MAJOR if a_inner else _lib.MN_MAJOR
+    p.b_major = _lib.MN_MAJOR if b_inner else _lib.K_MAJOR
+    p.in_dtype = _DTYPE[A.dtype]
+    p.out_dtype = _DTYPE[C.dtype]
+    p.algo = _ALGO[algo] if isinstance(algo, str) else int(algo)
+    p.depth = int(depth)
+    p.beta = int(beta)
+    p.prod_dtype = -1 if prod_dtype is None else _DTYPE[prod_dtype]
+    p.precision = _lib.PREC_3XTF32 if precision == "3xtf32" else _lib.PREC_TF32
+    p.tile_variant = int(tile_variant)
+    return p, A2, B2
+
+
+def workspace_bytes(p: "_lib.Problem") -> int:
+    n = ctypes.c_size_t(0)
+    _lib.check(_lib.load().b200s_workspace_bytes(ctypes.byref(p), ctypes.byref(n)))
+    return n.value
+
+
+def resolve(p: "_lib.Problem"):
+    a, d = ctypes.c_int32(0), ctypes.c_int32(0)
+    _lib.check(_lib.load().b200s_resolve(ctypes.byref(p), ctypes.byref(a), ctypes.byref(d)))
+    return a.value, d.value
+
+
+def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto", depth=-1, beta=0,
+               prod_dtype=None, precision="tf32", tile_variant=0,
+               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ B (beta=0) or C += A @ B (beta=1) on the current CUDA stream. Returns C."""
+    _require_cuda(A, B, C)
+    lib = _lib.load()
+    p, A2, B2 = make_problem(A, B, C, algo, depth, beta, prod_dtype, precision, tile_variant)
+    with torch.cuda.device(C.device):
+        need = workspace_bytes(p)
+        ws_ptr = None
+        if need:
+            if workspace is None or workspace.numel() * workspace.element_size() < need:
+                workspace = torch.empty(need, dtype=torch.uint8, device=C.device)
+            ws_ptr = workspace.data_ptr()
+        stream = torch.cuda.current_stream(C.device).cuda_stream
+        rc = lib.b200s_matmul(ctypes.byref(p), A2.data_ptr(), B2.data_ptr(), C.data_ptr(), ws_ptr,
+                              need if need else 0, stream)
+        _lib.check(rc)
+        if workspace is not None:
+            workspace.record_stream(torch.cuda.current_stream(C.device))
+    return C
+
+
+def matmul(A: torch.Tensor, B: torch.Tensor, *, algo="auto", depth=-1, out_dtype=None, prod_dtype=None,
+           precision="tf32", tile_variant=0, workspace=None) -> torch.Tensor:
+    """A @ B as a new tensor of ``out_dtype`` (default: the operand dtype)."""
+    _require_cuda(A, B)
+    shape = (A.shape[-2], B.shape[-1]) if A.dim() == 2 else (A.shape[0], A.shape[-2], B.shape[-1])
+    C = torch.empty(shape, dtype=out_dtype or A.dtype, device=A.device)
+    return matmul_out(A, B, C, algo=algo, depth=depth, beta=0, prod_dtype=prod_dtype, precision=precision,
+                      tile_variant=tile_variant, workspace=workspace)
+
+
+def device_status(device=None):
+    """(status, detail) of the device status word; synchronises the current stream."""
+    lib = _lib.load()
+    s, d = ctypes.c_int32(0), ctypes.c_int32(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.b200s_device_status(stream, ctypes.byref(s), ctypes.byref(d)))
+    return s.value, d.value
+
+
+class _MatmulFn(torch.autograd.Function):
+    """Y = X @ W with dX = dY @ W^T and dW = X^T @ dY through the same entry point. The
+    reference has no custom Function: autograd differentiates its slice/add/mm graph
+    (fixed_strassen_fp32_agg.py:13-125), which computes these same two products."""
+
+    @staticmethod
+    def forward(ctx, X, W, algo, depth, prod_dtype):
+        ctx.save_for_backward(X, W)
+        ctx.cfg = (algo, depth, prod_dtype)
+        return matmul(X, W, algo=algo, depth=depth, prod_dtype=prod_dtype)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, W = ctx.saved_tensors
+        algo, depth, prod_dtype = ctx.cfg
+        dX = dW = None
+        if dY.dtype != X.dtype:
+            dY = dY.to(X.dtype)
+        if ctx.needs_input_grad[0]:
+            dX = matmul(dY, W.transpose(-1, -2), algo=algo, depth=depth, prod_dtype=prod_dtype)
+        if ctx.needs_input_grad[1]:
+            dW = matmul(X.transpose(-1, -2), dY, algo=algo, depth=depth, prod_dtype=prod_dtype)
+        return dX, dW, None, None, None
+
+
+def matmul_autograd(X, W, algo="auto", depth=-1, prod_dtype=None):
+    """Differentiable X @ W (2-D operands)."""
+    return _MatmulFn.apply(X, W, algo, depth, prod_dtype)
