@@ -246,6 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
@@ -294,6 +295,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (kCtaGroup == 2) ptx::umma_commit<kCtaGroup>(ptx::mapa_cluster(tfull_bar(buf), 1));
       }
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
