@@ -98,6 +98,7 @@ struct Plan {
   int64_t np;               // 7^depth
   int64_t Mb, Nb, Kb;       // block extents
   size_t sa_bytes, sb_bytes, mp_bytes;
+  size_t ta_bytes, tb_bytes;  // K-major copies of fp32 operands given MN-major
   size_t total_bytes;
 };
 
@@ -151,8 +152,15 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   plan->Mb = p->M / div;
   plan->Nb = p->N / div;
   plan->Kb = p->K / div;
+  plan->ta_bytes = plan->tb_bytes = 0;
+  if (p->in_dtype == B200S_FP32) {
+    const size_t b = static_cast<size_t>(p->batch);
+    if (p->a_major == B200S_MN_MAJOR) plan->ta_bytes = round256(b * p->M * p->K * 4);
+    if (p->b_major == B200S_MN_MAJOR) plan->tb_bytes = round256(b * p->K * p->N * 4);
+  }
   if (depth == 0) {
-    plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = plan->total_bytes = 0;
+    plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = 0;
+    plan->total_bytes = plan->ta_bytes + plan->tb_bytes;
     return B200S_OK;
   }
   const size_t es = dtype_size(p->in_dtype), ps = dtype_size(pd);
@@ -160,7 +168,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   plan->sa_bytes = round256(nb * plan->Mb * plan->Kb * es);
   plan->sb_bytes = round256(nb * plan->Kb * plan->Nb * es);
   plan->mp_bytes = round256(nb * plan->Mb * plan->Nb * ps);
-  plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes;
+  plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes + plan->ta_bytes + plan->tb_bytes;
   return B200S_OK;
 }
 
@@ -288,12 +296,14 @@ int b200s_combine(const b200s_problem* p, const void* products, void* C, void* s
   return launch_combine(c, static_cast<cudaStream_t>(stream));
 }
 
-int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, void* workspace,
+int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* workspace,
                  size_t workspace_bytes, void* stream_v) {
-  if (!p || !A || !B || !C) return B200S_ERR_NULL_POINTER;
+  if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;
   Plan plan;
-  int rc = make_plan(p, &plan);
+  int rc = make_plan(p_in, &plan);
   if (rc) return rc;
+  b200s_problem local = *p_in;
+  b200s_problem* p = &local;
   if (plan.total_bytes > 0) {
     if (!workspace) return B200S_ERR_NULL_POINTER;
     if (workspace_bytes < plan.total_bytes) return B200S_ERR_WORKSPACE_TOO_SMALL;
@@ -301,6 +311,24 @@ int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, 
   }
   if (!device_status_words()) return B200S_ERR_NO_DEVICE;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (plan.ta_bytes) {
+    // fp32 A given K x M: rewrite it M x K
+    void* At = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes;
+    rc = launch_transpose_f32(A, At, p->K, p->M, p->lda, p->K, p->batch, p->strideA, p->M * p->K, stream);
+    if (rc) return rc;
+    A = At;
+    p->a_major = B200S_K_MAJOR, p->lda = p->K, p->strideA = p->M * p->K;
+  }
+  if (plan.tb_bytes) {
+    // fp32 B given K x N: rewrite it N x K
+    void* Bt = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes + plan.ta_bytes;
+    rc = launch_transpose_f32(B, Bt, p->K, p->N, p->ldb, p->K, p->batch, p->strideB, p->K * p->N, stream);
+    if (rc) return rc;
+    B = Bt;
+    p->b_major = B200S_K_MAJOR, p->ldb = p->K, p->strideB = p->K * p->N;
+  }
 
   GemmArgs g;
   g.cta_group = p->tile_variant;
@@ -318,7 +346,6 @@ int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, 
     return launch_gemm(g, stream);
   }
 
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
   void* Sa = ws;
   void* Sb = ws + plan.sa_bytes;
   void* Mp = ws + plan.sa_bytes + plan.sb_bytes;

@@ -44,6 +44,11 @@ struct GemmArgs {
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 
+// ---- fp32 operand re-layout (transpose.cu) -----------------------------------------------
+// out[c][r] = in[r][c] for a rows x cols fp32 matrix per batch item.
+int launch_transpose_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                         int64_t batch, int64_t stride_in, int64_t stride_out, cudaStream_t stream);
+
 // ---- Strassen schedule (schedule.h) and its passes (preadd.cu, combine.cu) ----------------
 struct PreaddArgs {
   const void* X;   // one operand, storage rows x cols with the contiguous dimension last

@@ -1,0 +1,320 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the reference's own outputs.
+
+Tolerances (relative Frobenius norm unless stated):
+  * against ``library_model`` (same rounding points, exact products): 1e-3 for bf16/fp16 - five
+    times below the algorithm's own error, so a wrong sign or block would show; 2e-3 for TF32.
+  * against fp64: the CUDA result may not be worse than the reference's genuine paths at the same
+    depth and dtype (fixed_strassen, and fp32-agg with base_dtype forwarded), with 5 % slack.
+  * against the committed reference outputs: the two results carry independent rounding, so the
+    bound is 1.5 x the sum of the two errors against fp64.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import strassen_oracle as so
+from tests.conftest import seeded_pair
+from tests.golden.make_golden import CASES, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz")
+
+
+@pytest.fixture(scope="module")
+def ops(built_library):
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device")
+    from strassen_triton_b200 import ops as _ops
+
+    return _ops
+
+
+def rel(x, ref):
+    return ((x.double() - ref.double()).norm() / ref.double().norm()).item()
+
+
+def status_ok(ops):
+    assert ops.device_status() == (0, 0)
+
+
+# ------------------------------------------------------------------ dense product
+
+EDGE = [127, 128, 129, 257, 300]
+
+
+@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("M", EDGE)
+@pytest.mark.parametrize("N", [256, 264, 520])
+def test_dense_tile_edges(ops, tile_variant, M, N):
+    """All remainders around the 128/256 tile edges; K with a ragged last block."""
+    for K in (64, 72, 200):
+        A, B = seeded_pair(M * 7 + N + K, (M, K), (K, N))
+        A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+        C = ops.matmul(A, B, algo="dense", tile_variant=tile_variant, out_dtype=torch.float32)
+        ref = A.double() @ B.double()
+        assert rel(C, ref) < 2e-6, (M, N, K)
+    status_ok(ops)
+
+
+@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dense_operand_majors(ops, tile_variant, a_t, b_t, dtype):
+    M, N, K = 384, 512, 320
+    A, B = seeded_pair(11, (M, K), (K, N))
+    A, B = A.to(dtype).cuda(), B.to(dtype).cuda()
+    Av = A.t().contiguous().t() if a_t else A
+    Bv = B.t().contiguous().t() if b_t else B
+    C = ops.matmul(Av, Bv, algo="dense", tile_variant=tile_variant, out_dtype=torch.float32)
+    assert rel(C, A.double() @ B.double()) < 2e-6
+    status_ok(ops)
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_dense_tf32_all_majors(ops, a_t, b_t):
+    """fp32 operands run as TF32; operands whose outer dimension is contiguous are re-laid out
+    by the library's transpose pass first."""
+    A, B = seeded_pair(3, (512, 256), (256, 384))
+    A, B = A.cuda(), B.cuda()
+    Av = A.t().contiguous().t() if a_t else A
+    Bv = B.t().contiguous().t() if b_t else B
+    C = ops.matmul(Av, Bv, algo="dense")
+    assert rel(C, A.double() @ B.double()) < 2e-3  # 10-bit operand mantissa
+    C = ops.matmul(Av, Bv, algo="classic", depth=1)
+    assert rel(C, A.double() @ B.double()) < 4e-3
+    status_ok(ops)
+
+
+def test_dense_batched_and_beta(ops):
+    A, B = seeded_pair(5, (3, 256, 192), (3, 192, 320))
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    C = torch.zeros(3, 256, 320, device="cuda", dtype=torch.float32)
+    ops.matmul_out(A, B, C, algo="dense", beta=1)
+    ops.matmul_out(A, B, C, algo="dense", beta=1)
+    ref = torch.bmm(A.double(), B.double())
+    assert rel(C, 2 * ref) < 2e-6
+    status_ok(ops)
+
+
+# ------------------------------------------------------------------ Strassen vs the oracle
+
+@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("algo", ["classic", "winograd"])
+@pytest.mark.parametrize("depth", [1, 2])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_strassen_matches_library_model(ops, tile_variant, algo, depth, dtype):
+    n = 512
+    A, B = seeded_pair(0, (n, n), (n, n), scale=n ** -0.5)
+    A, B = A.to(dtype), B.to(dtype)
+    want = so.library_model(A, B, depth, algo)
+    got = ops.matmul(A.cuda(), B.cuda(), algo=algo, depth=depth, tile_variant=tile_variant).cpu()
+    assert rel(got, want) < 1e-3
+    status_ok(ops)
+
+
+@pytest.mark.parametrize("shape", [(512, 256, 1024), (256, 768, 512), (1024, 512, 256)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False)])
+def test_strassen_rectangular_and_transposed(ops, shape, a_t, b_t):
+    M, N, K = shape
+    A, B = seeded_pair(M + N, (M, K), (K, N), dist="uniform")
+    A, B = A.bfloat16(), B.bfloat16()
+    want = so.library_model(A, B, 2, "classic", prod_dtype=torch.float32, out_dtype=torch.float32)
+    Ag, Bg = A.cuda(), B.cuda()
+    Ag = Ag.t().contiguous().t() if a_t else Ag
+    Bg = Bg.t().contiguous().t() if b_t else Bg
+    got = ops.matmul(Ag, Bg, algo="classic", depth=2, prod_dtype=torch.float32, out_dtype=torch.float32).cpu()
+    assert rel(got, want) < 1e-4   # fp32 products and output: only accumulation order differs
+    status_ok(ops)
+
+
+@pytest.mark.parametrize("depth", [1, 2])
+def test_error_is_no_worse_than_the_reference(ops, depth):
+    """Against fp64, at the same depth and dtype, on U(-1,1) bf16 inputs (BASELINE config 3's
+    distribution at a size the CPU oracle finishes in seconds)."""
+    n = 1024
+    A, B = seeded_pair(0, (n, n), (n, n), dist="uniform")
+    A, B = A.bfloat16(), B.bfloat16()
+    got = ops.matmul(A.cuda(), B.cuda(), algo="classic", depth=depth).cpu()
+    e_gpu = so.errors_vs_fp64(got, A, B)
+    e_plain = so.errors_vs_fp64(so.n_layers(A, B, depth, None, False), A, B)
+    e_agg = so.errors_vs_fp64(so.n_layers(A, B, depth, torch.bfloat16, True, True), A, B)
+    assert e_gpu[1] <= 1.05 * e_plain[1] and e_gpu[1] <= 1.05 * e_agg[1], (e_gpu, e_plain, e_agg)
+    assert e_gpu[0] <= 1.5 * max(e_plain[0], e_agg[0])
+    status_ok(ops)
+
+
+def _from_numpy(arr, dtype_name):
+    if "bfloat16" in dtype_name:
+        return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
+    if "float16" in dtype_name:
+        return torch.from_numpy(arr.view(np.int16).copy()).view(torch.float16)
+    return torch.from_numpy(arr.copy())
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c[5] >= 64], ids=[c[0] for c in CASES if c[5] >= 64])
+def test_against_committed_reference_outputs(ops, case):
+    """The reference's own outputs (made by tests/golden/make_golden.py) on the same seeded inputs."""
+    name, mod, fn, kwargs, seed, n, dtype, dist = case
+    data = np.load(GOLDEN)
+    want = _from_numpy(data[name], str(data[name + "__dtype"]))
+    A, B = make_inputs(seed, n, dtype, dist)
+    depth = 1 if fn == "_strassen_base" else min(kwargs.get("n_depth", 2), 2)
+    base = kwargs.get("base_dtype", None)
+    Ag, Bg = A.cuda(), B.cuda()
+    if base is not None and base != dtype:
+        Ag, Bg = Ag.to(base), Bg.to(base)
+    got = ops.matmul(Ag, Bg, algo="classic", depth=depth).cpu()
+    e_ref = so.errors_vs_fp64(want, A, B)[1]
+    e_gpu = so.errors_vs_fp64(got, A, B)[1]
+    floor = 2e-3 if got.dtype == torch.float32 else 0.0   # fp32 inputs run as TF32 on the tensor cores
+    assert rel(got, want) <= 1.5 * (e_ref + e_gpu) + floor
+    assert e_gpu <= max(1.3 * e_ref, floor), (e_gpu, e_ref)
+    status_ok(ops)
+
+
+# ------------------------------------------------------------------ reference-named entry points
+
+def test_run_launchers_accumulate_and_return_none(ops):
+    import strassen
+    import strassen_2_layer
+
+    n = 512
+    A, B = seeded_pair(1234, (n, n), (n, n), scale=n ** -0.5)
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    ref = A.double() @ B.double()
+    for fn, tol in ((strassen.run_matmul_fp32_accum, 1e-5), (strassen.run_strassen, 2e-2), (strassen.run_strassen2, 3e-2),
+                    (strassen.run_winograd_strassen, 3e-2), (strassen_2_layer.run_strassen_2_layer_fp32_accum, 3e-2)):
+        C = torch.zeros(n, n, device="cuda", dtype=torch.float32)
+        assert fn(A, B, C) is None
+        assert fn(A, B, C) is None
+        assert rel(C, 2 * ref) < tol, fn.__name__
+    # batched (3-D) form of the run_* launchers
+    A3, B3 = A.view(2, 256, 512).contiguous(), B.unsqueeze(0).expand(2, n, n).contiguous()
+    C3 = torch.zeros(2, 256, n, device="cuda", dtype=torch.float32)
+    strassen.run_strassen(A3, B3, C3)
+    assert rel(C3, torch.bmm(A3.double(), B3.double())) < 2e-2
+    status_ok(ops)
+
+
+def test_functional_entry_points(ops):
+    import fixed_strassen
+    import fixed_strassen_fp32_agg as agg
+    import strassen
+
+    n = 512
+    A, B = seeded_pair(3331, (n, n), (n, n), scale=n ** -0.5)
+    Ab, Bb = A.bfloat16().cuda(), B.bfloat16().cuda()
+    ref = Ab.double() @ Bb.double()
+    C = agg.strassen_matmul_n_layers(Ab, Bb, 2, torch.bfloat16)
+    assert C.dtype == torch.bfloat16 and rel(C, ref) < 2e-2
+    C = agg.strassen_matmul_n_layers(Ab, Bb)          # default base_dtype: fp32 result, as in the reference
+    assert C.dtype == torch.float32 and rel(C, ref) < 3e-3
+    C = agg._strassen_base(Ab, Bb, torch.bfloat16)
+    assert C.dtype == torch.bfloat16 and rel(C, ref) < 1e-2
+    C = fixed_strassen.strassen_matmul_n_layers(Ab, Bb, n_depth=3)   # deeper requests run two levels
+    assert C.dtype == torch.bfloat16 and rel(C, ref) < 2e-2
+    C = strassen.strassen_matmul_two_layers(Ab, Bb)
+    assert C.dtype == torch.bfloat16 and rel(C, ref) < 2e-2
+    small = torch.randn(16, 16, device="cuda")
+    assert rel(strassen._strassen_base(small, small), small.double() @ small.double()) < 2e-3
+    status_ok(ops)
+
+
+# ------------------------------------------------------------------ LinearStrassen forward / backward
+
+@pytest.mark.parametrize("shape", [(8192, 768, 3072), (8192, 3072, 768), (8192, 768, 2304), (2048, 2048, 2048)])
+@pytest.mark.parametrize("depth", [0, 1])
+def test_linear_forward_backward(ops, shape, depth):
+    """BASELINE config 4: X ~ N(0,1), W ~ N(0, 0.02), dY ~ N(0,1); Y, dX, dW against fp64 autograd."""
+    from model.layers import LinearStrassen
+
+    M, din, dout = shape
+    g = torch.Generator("cpu").manual_seed(0)
+    X = torch.randn(M, din, generator=g)
+    W = torch.randn(dout, din, generator=g) * 0.02
+    dY = torch.randn(M, dout, generator=g)
+    layer = LinearStrassen(din, dout, bias=True, dtype=torch.bfloat16, depth=depth, device="cuda")
+    with torch.no_grad():
+        layer.weight.copy_(W)
+        layer.bias.zero_()
+    x = X.bfloat16().cuda().requires_grad_(True)
+    y = layer(x)
+    y.backward(dY.bfloat16().cuda())
+    Xd, Wd, dYd = X.bfloat16().double().cuda(), W.bfloat16().double().cuda(), dY.bfloat16().double().cuda()
+    tol = 5e-3 if depth == 0 else 1.2e-2
+    assert rel(y, Xd @ Wd.t()) < tol
+    assert rel(x.grad, dYd @ Wd) < tol
+    assert rel(layer.weight.grad, dYd.t() @ Xd) < tol
+    assert rel(layer.bias.grad, dYd.sum(0)) < 5e-3
+    status_ok(ops)
+
+
+def test_linear_under_autocast(ops):
+    from model.layers import LinearStrassen
+
+    layer = LinearStrassen(512, 512, bias=False, dtype=torch.float32, depth=1, device="cuda")
+    x = torch.randn(4, 128, 512, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = layer(x)
+    assert y.dtype == torch.bfloat16 and y.shape == (4, 128, 512)
+    y.float().sum().backward()
+    assert layer.weight.grad is not None and layer.weight.grad.dtype == torch.float32
+    ref = x.detach().double().view(-1, 512) @ layer.weight.detach().double().t()
+    assert rel(y.view(-1, 512), ref) < 1.5e-2
+    status_ok(ops)
+
+
+# ------------------------------------------------------------------ full-size properties
+
+@pytest.mark.parametrize("n,depth,algo,dist", [
+    (8192, 1, "classic", "normal_scaled"),     # BASELINE config 2
+    (8192, 1, "winograd", "normal_scaled"),
+    (16384, 2, "classic", "uniform"),          # BASELINE config 3
+    (16384, 0, "dense", "uniform"),
+])
+def test_full_size_probe_vector_and_cublas(ops, n, depth, algo, dist):
+    """At BASELINE sizes the oracle is too slow; C is checked through C.x = A.(B.x) for random x
+    in fp64 (linear in every entry of C) and against cuBLAS on the same inputs."""
+    g = torch.Generator("cpu").manual_seed(0)
+    if dist == "uniform":
+        A = (2 * torch.rand((n, n), generator=g) - 1).bfloat16().cuda()
+        B = (2 * torch.rand((n, n), generator=g) - 1).bfloat16().cuda()
+    else:
+        A = (torch.randn((n, n), generator=g) / n ** 0.5).bfloat16().cuda()
+        B = (torch.randn((n, n), generator=g) / n ** 0.5).bfloat16().cuda()
+    C = ops.matmul(A, B, algo=algo, depth=depth)
+    torch.cuda.synchronize()
+    x = torch.randn(n, 8, device="cuda", dtype=torch.float64, generator=torch.Generator("cuda").manual_seed(1))
+    want = A.double() @ (B.double() @ x)
+    got = C.double() @ x
+    bound = {0: 3e-3, 1: 1e-2, 2: 2e-2}[depth] * (1.7 if algo == "winograd" else 1.0)
+    assert rel(got, want) < bound
+    dense = torch.mm(A, B)
+    assert rel(C, dense) < bound + 3e-3
+    # determinism: the pipeline has no atomics, so a second run is bit-identical
+    C2 = ops.matmul(A, B, algo=algo, depth=depth)
+    assert torch.equal(C, C2)
+    status_ok(ops)
+
+
+# ------------------------------------------------------------------ host-side error paths on a GPU box
+
+def test_workspace_too_small_raises(ops):
+    from strassen_triton_b200 import _lib
+
+    A = torch.zeros(512, 512, device="cuda", dtype=torch.bfloat16)
+    C = torch.empty_like(A)
+    p, A2, B2 = ops.make_problem(A, A, C, "classic", 2)
+    need = ops.workspace_bytes(p)
+    ws = torch.empty(need - 256, dtype=torch.uint8, device="cuda")
+    rc = _lib.load().b200s_matmul(ctypes.byref(p), A.data_ptr(), A.data_ptr(), C.data_ptr(), ws.data_ptr(),
+                                 need - 256, torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.ERR_WORKSPACE_TOO_SMALL
+    with pytest.raises(ValueError):
+        ops.matmul(torch.zeros(500, 500, device="cuda", dtype=torch.bfloat16),
+                   torch.zeros(500, 500, device="cuda", dtype=torch.bfloat16), algo="classic", depth=2)
+    assert _lib.load().b200s_launch_count() > 0
