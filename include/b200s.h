@@ -85,7 +85,12 @@ typedef struct b200s_problem {
                          point: torch.mm returns the input dtype). -1 = same as in_dtype */
   int32_t precision;  /* b200s_precision, used when in_dtype is fp32 */
   int32_t tile_variant; /* GEMM tile shape: 0 = library default, 1 = one CTA per 128x256 tile,
-                         2 = a CTA pair per 256x256 tile (tcgen05 cta_group::2) */
+                         2 = a CTA pair per 256x256 tile (tcgen05 cta_group::2, accumulators
+                         double-buffered), 3 = a CTA pair per 256x512 tile */
+  int32_t pipeline;   /* how the Strassen passes are scheduled: 0 = library decides, 1 = pipelined
+                         (operand sums and recombination run on side streams beside the products,
+                         outer group by outer group), 2 = sequential on the caller's stream */
+  int32_t reserved;
 } b200s_problem;
 
 /* Library version, major*10000 + minor*100 + patch. */

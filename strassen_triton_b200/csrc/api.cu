@@ -27,6 +27,11 @@ struct DeviceState {
   bool ok = false;
   int sms = 0;
   uint32_t* status = nullptr;
+  // Pipelined driver: side streams and events, created on the first pipelined call.
+  std::mutex pipe_mu;
+  bool pipe_ready = false;
+  cudaStream_t s_add = nullptr, s_gemm = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_end = nullptr, ev_pre[7] = {}, ev_done[7] = {};
 };
 std::mutex g_dev_mu;
 DeviceState g_dev[64];
@@ -113,6 +118,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   if (p->algo < B200S_ALGO_AUTO || p->algo > B200S_ALGO_WINOGRAD) return B200S_ERR_BAD_ALGO;
   if (p->depth < -1 || p->depth > 2) return B200S_ERR_BAD_DEPTH;
   if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
+  if (p->pipeline < 0 || p->pipeline > 2) return B200S_ERR_BAD_SHAPE;
   const int64_t a_cols = p->a_major == B200S_K_MAJOR ? p->K : p->M;
   const int64_t b_cols = p->b_major == B200S_K_MAJOR ? p->K : p->N;
   if (p->lda < a_cols || p->ldb < b_cols || p->ldc < p->N) return B200S_ERR_BAD_STRIDE;
@@ -169,6 +175,113 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   plan->sb_bytes = round256(nb * plan->Kb * plan->Nb * es);
   plan->mp_bytes = round256(nb * plan->Mb * plan->Nb * ps);
   plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes + plan->ta_bytes + plan->tb_bytes;
+  return B200S_OK;
+}
+
+// Order in which the outer products are formed and multiplied, chosen so that the outer quadrants
+// of C complete one after another (classic: C11 after 4 groups, then C12, C21, C22).
+const int kOrderClassic[7] = {0, 3, 4, 6, 2, 1, 5};
+const int kOrderWinograd[7] = {0, 1, 4, 5, 2, 6, 3};
+
+int ensure_pipe(DeviceState* ds) {
+  if (ds->pipe_ready) return B200S_OK;
+  int lo = 0, hi = 0;
+  B200S_CUDA_OK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  B200S_CUDA_OK(cudaStreamCreateWithPriority(&ds->s_gemm, cudaStreamNonBlocking, hi));
+  B200S_CUDA_OK(cudaStreamCreateWithPriority(&ds->s_add, cudaStreamNonBlocking, lo));
+  B200S_CUDA_OK(cudaEventCreateWithFlags(&ds->ev_start, cudaEventDisableTiming));
+  B200S_CUDA_OK(cudaEventCreateWithFlags(&ds->ev_end, cudaEventDisableTiming));
+  for (int i = 0; i < 7; ++i) {
+    B200S_CUDA_OK(cudaEventCreateWithFlags(&ds->ev_pre[i], cudaEventDisableTiming));
+    B200S_CUDA_OK(cudaEventCreateWithFlags(&ds->ev_done[i], cudaEventDisableTiming));
+  }
+  ds->pipe_ready = true;
+  return B200S_OK;
+}
+
+// Strassen with the outer level software-pipelined over three streams: the bandwidth-bound
+// operand sums of group i+1.. and the recombination of finished quadrants run beside the
+// tensor-core-bound products of group i. Scratch blocks are laid out in processing order.
+int run_pipelined(const b200s_problem* p, const Plan& plan, const void* A, const void* B, void* C, void* Sa, void* Sb,
+                  void* Mp, cudaStream_t user) {
+  DeviceState* ds = current_device_state();
+  if (!ds || !ds->ok) return B200S_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(ds->pipe_mu);
+  int rc = ensure_pipe(ds);
+  if (rc) return rc;
+  const bool wino = plan.algo == B200S_ALGO_WINOGRAD;
+  const int* order = wino ? kOrderWinograd : kOrderClassic;
+  const int sa = wino ? sched::kWinograd : sched::kClassic;
+  const int np2 = static_cast<int>(plan.np / 7);  // products per outer group
+  int pos[7];
+  for (int i = 0; i < 7; ++i) pos[order[i]] = i;
+  const size_t es = dtype_size(p->in_dtype), ps = dtype_size(plan.prod_dtype);
+  const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+
+  B200S_CUDA_OK(cudaEventRecord(ds->ev_start, user));
+  B200S_CUDA_OK(cudaStreamWaitEvent(ds->s_add, ds->ev_start, 0));
+  B200S_CUDA_OK(cudaStreamWaitEvent(ds->s_gemm, ds->ev_start, 0));
+
+  for (int i = 0; i < 7; ++i) {
+    PreaddOuterArgs pa;
+    pa.batch = 1;
+    pa.algo = plan.algo, pa.depth = plan.depth, pa.dtype = p->in_dtype;
+    pa.n_groups = 1;
+    pa.groups[0] = order[i];
+    pa.out_block0[0] = i * np2;
+    pa.X = A, pa.out = Sa, pa.side = 0;
+    pa.rows_blk = a_k ? plan.Mb : plan.Kb, pa.cols_blk = a_k ? plan.Kb : plan.Mb;
+    pa.ld = p->lda, pa.strideX = 0, pa.transposed = !a_k;
+    rc = launch_preadd_outer(pa, ds->s_add);
+    if (rc) return rc;
+    pa.X = B, pa.out = Sb, pa.side = 1;
+    pa.rows_blk = b_k ? plan.Nb : plan.Kb, pa.cols_blk = b_k ? plan.Kb : plan.Nb;
+    pa.ld = p->ldb, pa.transposed = b_k;
+    rc = launch_preadd_outer(pa, ds->s_add);
+    if (rc) return rc;
+    B200S_CUDA_OK(cudaEventRecord(ds->ev_pre[i], ds->s_add));
+  }
+
+  int last_pos[4];
+  for (int r = 0; r < 4; ++r) {
+    last_pos[r] = 0;
+    for (int p1 = 0; p1 < 7; ++p1)
+      if (sched::w1(sa, r, p1) != 0 && pos[p1] > last_pos[r]) last_pos[r] = pos[p1];
+  }
+
+  for (int i = 0; i < 7; ++i) {
+    B200S_CUDA_OK(cudaStreamWaitEvent(ds->s_gemm, ds->ev_pre[i], 0));
+    GemmArgs g;
+    g.cta_group = p->tile_variant;
+    g.in_dtype = p->in_dtype, g.a_major = p->a_major, g.b_major = p->b_major;
+    g.A = static_cast<const uint8_t*>(Sa) + static_cast<size_t>(i) * np2 * plan.Mb * plan.Kb * es;
+    g.B = static_cast<const uint8_t*>(Sb) + static_cast<size_t>(i) * np2 * plan.Kb * plan.Nb * es;
+    g.C = static_cast<uint8_t*>(Mp) + static_cast<size_t>(i) * np2 * plan.Mb * plan.Nb * ps;
+    g.M = plan.Mb, g.N = plan.Nb, g.K = plan.Kb, g.batch = np2;
+    g.lda = a_k ? plan.Kb : plan.Mb, g.ldb = b_k ? plan.Kb : plan.Nb, g.ldc = plan.Nb;
+    g.strideA = plan.Mb * plan.Kb, g.strideB = plan.Kb * plan.Nb, g.strideC = plan.Mb * plan.Nb;
+    g.out_dtype = plan.prod_dtype, g.beta = 0;
+    rc = launch_gemm(g, ds->s_gemm);
+    if (rc) return rc;
+    B200S_CUDA_OK(cudaEventRecord(ds->ev_done[i], ds->s_gemm));
+
+    CombineOuterArgs ca;
+    ca.n_quads = 0;
+    for (int r = 0; r < 4; ++r)
+      if (last_pos[r] == i) ca.quads[ca.n_quads++] = r;
+    if (ca.n_quads == 0) continue;
+    ca.products = Mp, ca.C = C;
+    ca.Mb = plan.Mb, ca.Nb = plan.Nb, ca.ldc = p->ldc, ca.batch = 1, ca.strideC = 0;
+    ca.algo = plan.algo, ca.depth = plan.depth, ca.prod_dtype = plan.prod_dtype, ca.out_dtype = p->out_dtype;
+    ca.beta = p->beta;
+    for (int p1 = 0; p1 < 7; ++p1) ca.group_block0[p1] = pos[p1] * np2;
+    // the products stream is in order, so this event also covers every earlier group
+    B200S_CUDA_OK(cudaStreamWaitEvent(ds->s_add, ds->ev_done[i], 0));
+    rc = launch_combine_outer(ca, ds->s_add);
+    if (rc) return rc;
+  }
+  B200S_CUDA_OK(cudaEventRecord(ds->ev_end, ds->s_add));
+  B200S_CUDA_OK(cudaStreamWaitEvent(user, ds->ev_end, 0));
   return B200S_OK;
 }
 
@@ -332,7 +445,7 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
 
   GemmArgs g;
   g.cta_group = p->tile_variant;
-  if (g.cta_group < 0 || g.cta_group > 2) return B200S_ERR_BAD_SHAPE;
+  if (g.cta_group < 0 || g.cta_group > 3) return B200S_ERR_BAD_SHAPE;
   g.in_dtype = p->in_dtype;
   g.a_major = p->a_major;
   g.b_major = p->b_major;
@@ -349,6 +462,11 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   void* Sa = ws;
   void* Sb = ws + plan.sa_bytes;
   void* Mp = ws + plan.sa_bytes + plan.sb_bytes;
+
+  // Large single products run the pipelined driver unless the caller chose otherwise.
+  const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
+  const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 4096.0 * 4096.0 * 4096.0);
+  if (p->batch == 1 && pipelined) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 
   rc = b200s_preadd(p, 0, A, Sa, stream_v);
   if (rc) return rc;

@@ -214,6 +214,126 @@ int launch_dtype(const CombineArgs& a, cudaStream_t stream) {
   return B200S_ERR_BAD_DTYPE;
 }
 
+// ---- outer-quadrant form --------------------------------------------------------------------
+// One launch writes a few outer quadrants of C only, reading just the product groups that feed
+// them, so the pipelined driver can recombine a quadrant as soon as its last group is done.
+
+struct CombineOuterParams {
+  const void* products;
+  void* C;
+  int64_t Mb, nb_vec;       // finest block rows, 16-byte product vectors per finest block row
+  int64_t ldc, strideC;
+  int64_t batch_blocks;     // product blocks per batch item (7^depth)
+  int32_t out_dtype, beta, vec_ok;
+  int8_t quad[4];           // outer quadrant of each listed entry
+  int8_t coef[4][7];        // [listed entry][outer product p1]
+  int32_t group_block0[7];  // first product block of outer product p1
+};
+
+template <int INNER, int ALGO, typename TP>
+__global__ void __launch_bounds__(256, 3) combine_outer_kernel(const CombineOuterParams p) {
+  constexpr int VEC = PVec<TP>::N;
+  constexpr int NQ2 = INNER ? 4 : 1;
+  constexpr int NP2 = INNER ? 7 : 1;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.Mb * p.nb_vec) return;
+  const int64_t row = idx / p.nb_vec;
+  const int64_t cv = idx - row * p.nb_vec;
+  const int64_t Nb = p.nb_vec * VEC;
+  const int64_t blk_elems = p.Mb * Nb;
+  const int e = blockIdx.y;
+
+  float acc[NQ2][VEC];
+#pragma unroll
+  for (int r = 0; r < NQ2; ++r)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[r][i] = 0.f;
+
+  const TP* prod = static_cast<const TP*>(p.products) + static_cast<int64_t>(blockIdx.z) * p.batch_blocks * blk_elems +
+                   row * Nb + cv * VEC;
+#pragma unroll 1
+  for (int p1 = 0; p1 < 7; ++p1) {
+    const int c = p.coef[e][p1];
+    if (c == 0) continue;
+    const TP* g0 = prod + static_cast<int64_t>(p.group_block0[p1]) * blk_elems;
+    if constexpr (INNER) {
+      float part[NQ2][VEC];
+#pragma unroll
+      for (int r = 0; r < NQ2; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) part[r][i] = 0.f;
+      Combine<1, ALGO, TP>::all_products(g0, blk_elems, part, std::make_integer_sequence<int, NP2>{});
+#pragma unroll
+      for (int r = 0; r < NQ2; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[r][i] = c > 0 ? acc[r][i] + part[r][i] : acc[r][i] - part[r][i];
+    } else {
+      float x[VEC];
+      load_pvec<TP>(g0, x);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[0][i] = c > 0 ? acc[0][i] + x[i] : acc[0][i] - x[i];
+    }
+  }
+
+  const int r1 = p.quad[e];
+#pragma unroll
+  for (int r2 = 0; r2 < NQ2; ++r2) {
+    const int br = INNER ? 2 * (r1 >> 1) + (r2 >> 1) : (r1 >> 1);
+    const int bc = INNER ? 2 * (r1 & 1) + (r2 & 1) : (r1 & 1);
+    const int64_t off = static_cast<int64_t>(blockIdx.z) * p.strideC + (br * p.Mb + row) * p.ldc + bc * Nb + cv * VEC;
+    if (p.out_dtype == B200S_BF16)
+      store_out<__nv_bfloat16, VEC>(static_cast<__nv_bfloat16*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
+    else if (p.out_dtype == B200S_FP16)
+      store_out<__half, VEC>(static_cast<__half*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
+    else
+      store_out<float, VEC>(static_cast<float*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
+  }
+}
+
+template <int INNER, int ALGO, typename TP>
+int launch_outer_one(const CombineOuterArgs& a, cudaStream_t stream) {
+  constexpr int VEC = PVec<TP>::N;
+  CombineOuterParams kp;
+  kp.products = a.products;
+  kp.C = a.C;
+  kp.Mb = a.Mb;
+  kp.nb_vec = a.Nb / VEC;
+  kp.ldc = a.ldc;
+  kp.strideC = a.strideC;
+  kp.batch_blocks = sched::ipow(7, INNER + 1);
+  kp.out_dtype = a.out_dtype;
+  kp.beta = a.beta;
+  const size_t oes = dtype_size(a.out_dtype);
+  kp.vec_ok = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) && ((a.ldc * oes) % 16 == 0) &&
+              ((a.Nb * oes) % 16 == 0) && (a.batch == 1 || (a.strideC * oes) % 16 == 0);
+  for (int e = 0; e < a.n_quads; ++e) {
+    kp.quad[e] = static_cast<int8_t>(a.quads[e]);
+    for (int p1 = 0; p1 < 7; ++p1) kp.coef[e][p1] = static_cast<int8_t>(sched::w1(ALGO, a.quads[e], p1));
+  }
+  for (int p1 = 0; p1 < 7; ++p1) kp.group_block0[p1] = a.group_block0[p1];
+  const int64_t total = kp.Mb * kp.nb_vec;
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.n_quads), static_cast<unsigned>(a.batch));
+  combine_outer_kernel<INNER, ALGO, TP><<<grid, 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
+
+template <int INNER, int ALGO>
+int launch_outer_dtype(const CombineOuterArgs& a, cudaStream_t stream) {
+  switch (a.prod_dtype) {
+    case B200S_BF16:
+      return launch_outer_one<INNER, ALGO, __nv_bfloat16>(a, stream);
+    case B200S_FP16:
+      return launch_outer_one<INNER, ALGO, __half>(a, stream);
+    case B200S_FP32:
+      return launch_outer_one<INNER, ALGO, float>(a, stream);
+  }
+  return B200S_ERR_BAD_DTYPE;
+}
+
 }  // namespace
 
 int launch_combine(const CombineArgs& a, cudaStream_t stream) {
@@ -228,6 +348,25 @@ int launch_combine(const CombineArgs& a, cudaStream_t stream) {
     return wino ? launch_dtype<1, sched::kWinograd>(a, stream) : launch_dtype<1, sched::kClassic>(a, stream);
   if (a.depth == 2)
     return wino ? launch_dtype<2, sched::kWinograd>(a, stream) : launch_dtype<2, sched::kClassic>(a, stream);
+  return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s
+
+namespace b200s {
+
+int launch_combine_outer(const CombineOuterArgs& a, cudaStream_t stream) {
+  const size_t pes = dtype_size(a.prod_dtype);
+  const int vec = static_cast<int>(16 / pes);
+  if (a.Mb <= 0 || a.Nb <= 0 || a.batch <= 0 || a.n_quads <= 0 || a.n_quads > 4) return B200S_ERR_BAD_SHAPE;
+  if (a.Nb % vec) return B200S_ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(a.products) & 15u) return B200S_ERR_BAD_ALIGNMENT;
+  const bool wino = a.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && a.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (a.depth == 1)
+    return wino ? launch_outer_dtype<0, sched::kWinograd>(a, stream) : launch_outer_dtype<0, sched::kClassic>(a, stream);
+  if (a.depth == 2)
+    return wino ? launch_outer_dtype<1, sched::kWinograd>(a, stream) : launch_outer_dtype<1, sched::kClassic>(a, stream);
   return B200S_ERR_BAD_DEPTH;
 }
 

@@ -40,7 +40,7 @@ struct GemmArgs {
   int a_major, b_major;
   int in_dtype, out_dtype;
   int beta;
-  int cta_group;  // 0 = default, 1 or 2 = force
+  int cta_group;  // tile variant of b200s_problem: 0 = default, 1..3 = force
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 
@@ -70,5 +70,32 @@ struct CombineArgs {
   int algo, depth, prod_dtype, out_dtype, beta;
 };
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
+
+
+// Outer-group forms used by the pipelined driver (api.cu): operand blocks of a few outer products,
+// and recombination of a few outer quadrants of C. Block positions in scratch are given
+// explicitly so the driver can lay groups out in processing order.
+struct PreaddOuterArgs {
+  const void* X;
+  void* out;
+  int64_t rows_blk, cols_blk;  // extents of one finest block in storage orientation
+  int64_t ld, batch, strideX;
+  int transposed, side, algo, depth, dtype;
+  int n_groups;
+  int groups[7];      // outer product indices p1 to form
+  int out_block0[7];  // first output block of each
+};
+int launch_preadd_outer(const PreaddOuterArgs& a, cudaStream_t stream);
+
+struct CombineOuterArgs {
+  const void* products;
+  void* C;
+  int64_t Mb, Nb, ldc, batch, strideC;
+  int algo, depth, prod_dtype, out_dtype, beta;
+  int n_quads;
+  int quads[4];         // outer quadrants of C to write
+  int group_block0[7];  // first product block of outer product p1
+};
+int launch_combine_outer(const CombineOuterArgs& a, cudaStream_t stream);
 
 }  // namespace b200s

@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.h"
@@ -34,16 +35,17 @@ namespace {
 
 constexpr int kBM = 128;          // accumulator rows per CTA (TMEM lanes)
 constexpr int kRowBytes = 128;    // bytes of one swizzled smem row = one K block of a K-major tile
-constexpr int kThreads = 192;
 
 struct GemmKernelParams {
   int32_t M, N;               // extents of one C[b]
   int32_t m_tiles, n_tiles;   // tiles per batch item
   int32_t k_blocks;
   int32_t total_tiles;
+  int32_t raster_group;       // m-tiles that share a band of n-tiles in the tile order
   int32_t a_mn, b_mn;
   int32_t fmt;                // operand format field of the instruction descriptor
   int32_t out_dtype, beta;
+  int32_t tma_store;          // 1: the epilogue stages tiles in shared memory and stores them with TMA
   int64_t ldc, strideC;
   void* C;
   uint32_t* status;
@@ -54,7 +56,7 @@ enum : uint32_t { kWhoProducer = 1, kWhoMma = 2, kWhoMmaAcc = 3, kWhoEpilogue = 
 
 __device__ __forceinline__ void decode_tile(const GemmKernelParams& p, int tile, int& b, int& mt,
                                             int& nt) {
-  constexpr int kGroup = 8;  // m-tiles per L2 group
+  const int kGroup = p.raster_group;
   const int per_batch = p.m_tiles * p.n_tiles;
   b = tile / per_batch;
   int t = tile - b * per_batch;
@@ -120,36 +122,48 @@ __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], 
   }
 }
 
-template <int kCtaGroup, int BN, int kStages, bool kTf32>
-__global__ void __launch_bounds__(kThreads, 1)
+// kNH = number of 256-column accumulator halves one tile owns.
+//   kNH == 1: tile N = 256, two accumulators used alternately, so the epilogue of tile i overlaps
+//             the main loop of tile i+1; 4 epilogue warps.
+//   kNH == 2: tile N = 512 (CTA pair: 256 x 512), both halves share each A block, which cuts the
+//             shared-memory fill traffic per flop by a quarter; the single accumulator set is
+//             drained by 8 epilogue warps before the next tile's first MMA.
+template <int kCtaGroup, int kNH, int kStages, bool kTf32>
+__global__ void __launch_bounds__(64 + 128 * kNH, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmKernelParams p) {
+            const __grid_constant__ CUtensorMap tmC, const GemmKernelParams p) {
   constexpr int ES = kTf32 ? 4 : 2;              // operand element size
   constexpr int BKE = kRowBytes / ES;            // K elements per stage
-  constexpr int BN_CTA = BN / kCtaGroup;         // B-tile rows this CTA loads
+  constexpr int BNH = 256;                       // columns of one accumulator half (one tcgen05.mma N)
+  constexpr int BN_TILE = BNH * kNH;             // columns of C one tile covers
+  constexpr int BNH_CTA = BNH / kCtaGroup;       // rows of one B half this CTA loads
   constexpr int A_BYTES = kBM * kRowBytes;
-  constexpr int B_BYTES = BN_CTA * kRowBytes;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int BH_BYTES = BNH_CTA * kRowBytes;  // one B half in this CTA's shared memory
+  constexpr int STAGE_BYTES = A_BYTES + kNH * BH_BYTES;
   constexpr int CHUNK_E = kRowBytes / ES;        // MN elements per 128-byte row of an MN-major tile
   constexpr int CHUNK_BYTES = BKE * kRowBytes;   // one MN-major chunk: BKE k-rows of 128 bytes
   constexpr int UMMA_K = 32 / ES;                // K elements per tcgen05.mma
   constexpr int K_STEPS = BKE / UMMA_K;          // = 4
-  constexpr uint32_t TMEM_COLS = 2 * BN;
-  static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+  constexpr int ACC_BUFS = kNH == 1 ? 2 : 1;     // accumulator sets in TMEM
+  constexpr int EPI_WARPS = 4 * kNH;
+  constexpr int STG_BUFS = kNH == 1 ? 2 : 1;     // 4 KB staging buffers per epilogue warp
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr int STAGING_BYTES = EPI_WARPS * STG_BUFS * 4096;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw);
 
-  // Barrier block lives after the stages.
-  const uint32_t bar_base = base + kStages * STAGE_BYTES;
+  // Stages, then the epilogue staging buffers, then the barriers.
+  const uint32_t staging_base = base + kStages * STAGE_BYTES;
+  const uint32_t bar_base = staging_base + STAGING_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
   volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(gbase + kStages * STAGE_BYTES + 8 * (2 * kStages + 4));
+      reinterpret_cast<volatile uint32_t*>(gbase + kStages * STAGE_BYTES + STAGING_BYTES + 8 * (2 * kStages + 4));
   volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -166,11 +180,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
-      ptx::mbar_init(tempty_bar(b), 4 * kCtaGroup);
+      ptx::mbar_init(tempty_bar(b), EPI_WARPS * kCtaGroup);
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
+    if (p.tma_store) ptx::prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     ptx::tmem_alloc<kCtaGroup>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -194,7 +209,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int b, mt, nt;
         decode_tile(p, tile, b, mt, nt);
         const int m0 = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM;
-        const int n0 = nt * BN + static_cast<int>(cta_rank) * BN_CTA;
+        const int n0 = nt * BN_TILE + static_cast<int>(cta_rank) * BNH_CTA;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!ptx::mbar_wait<kCtaGroup == 2>(empty_bar(stage), phase ^ 1u, abort_word, kWhoProducer)) {
             alive = false;
@@ -203,40 +218,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t sA = base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_BYTES;
           const int k0 = kb * BKE;
-          if constexpr (kCtaGroup == 1) {
-            const uint32_t fb = full_bar(stage);
-            ptx::mbar_expect_tx(fb, STAGE_BYTES);
-            if (!p.a_mn) {
-              ptx::tma_load_3d(sA, &tmA, fb, k0, m0, b);
-            } else {
-#pragma unroll
-              for (int j = 0; j < kBM / CHUNK_E; ++j)
-                ptx::tma_load_3d(sA + j * CHUNK_BYTES, &tmA, fb, m0 + j * CHUNK_E, k0, b);
-            }
-            if (!p.b_mn) {
-              ptx::tma_load_3d(sB, &tmB, fb, k0, n0, b);
-            } else {
-#pragma unroll
-              for (int j = 0; j < BN_CTA / CHUNK_E; ++j)
-                ptx::tma_load_3d(sB + j * CHUNK_BYTES, &tmB, fb, n0 + j * CHUNK_E, k0, b);
-            }
+          // With a CTA pair both CTAs' bytes are counted on the leader's barrier.
+          uint32_t fb = full_bar(stage);
+          if constexpr (kCtaGroup == 2) fb = ptx::mapa_cluster(fb, 0);
+          if (cta_rank == 0) ptx::mbar_expect_tx(full_bar(stage), kCtaGroup * STAGE_BYTES);
+          auto load = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
+            if constexpr (kCtaGroup == 2)
+              ptx::tma_load_3d_pair(dst, m, fb, c0, c1, b);
+            else
+              ptx::tma_load_3d(dst, m, fb, c0, c1, b);
+          };
+          if (!p.a_mn) {
+            load(sA, &tmA, k0, m0);
           } else {
-            // Both CTAs' bytes are counted on the leader's barrier.
-            const uint32_t fb = ptx::mapa_cluster(full_bar(stage), 0);
-            if (cta_rank == 0) ptx::mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-            if (!p.a_mn) {
-              ptx::tma_load_3d_pair(sA, &tmA, fb, k0, m0, b);
-            } else {
 #pragma unroll
-              for (int j = 0; j < kBM / CHUNK_E; ++j)
-                ptx::tma_load_3d_pair(sA + j * CHUNK_BYTES, &tmA, fb, m0 + j * CHUNK_E, k0, b);
-            }
+            for (int j = 0; j < kBM / CHUNK_E; ++j) load(sA + j * CHUNK_BYTES, &tmA, m0 + j * CHUNK_E, k0);
+          }
+#pragma unroll
+          for (int h = 0; h < kNH; ++h) {
+            const uint32_t sBh = sB + h * BH_BYTES;
+            const int nh = n0 + h * BNH;
             if (!p.b_mn) {
-              ptx::tma_load_3d_pair(sB, &tmB, fb, k0, n0, b);
+              load(sBh, &tmB, k0, nh);
             } else {
 #pragma unroll
-              for (int j = 0; j < BN_CTA / CHUNK_E; ++j)
-                ptx::tma_load_3d_pair(sB + j * CHUNK_BYTES, &tmB, fb, n0 + j * CHUNK_E, k0, b);
+              for (int j = 0; j < BNH_CTA / CHUNK_E; ++j) load(sBh + j * CHUNK_BYTES, &tmB, nh + j * CHUNK_E, k0);
             }
           }
           if (++stage == kStages) {
@@ -250,7 +256,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && cta_rank == 0) {
-      const uint32_t idesc = ptx::make_instr_desc(static_cast<uint32_t>(p.fmt), p.a_mn, p.b_mn, kBM * kCtaGroup, BN);
+      const uint32_t idesc =
+          ptx::make_instr_desc(static_cast<uint32_t>(p.fmt), p.a_mn, p.b_mn, kBM * kCtaGroup, BNH);
       // K-major: 8-row groups 1024 bytes apart, K advances 32 bytes inside the swizzled row.
       // MN-major: 8-k-row groups 1024 bytes apart (SBO), 128-byte MN chunks CHUNK_BYTES apart (LBO).
       const uint32_t a_lbo = p.a_mn ? CHUNK_BYTES : 16u, b_lbo = p.b_mn ? CHUNK_BYTES : 16u;
@@ -260,14 +267,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int it = 0;
       bool alive = true;
       for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters, ++it) {
-        const int buf = it & 1;
-        const uint32_t aphase = (it >> 1) & 1u;
+        const int buf = it % ACC_BUFS;
+        const uint32_t aphase = (it / ACC_BUFS) & 1u;
         if (!ptx::mbar_wait<kCtaGroup == 2>(tempty_bar(buf), aphase ^ 1u, abort_word, kWhoMmaAcc)) {
           alive = false;
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * BN);
+        const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * BN_TILE);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!ptx::mbar_wait<kCtaGroup == 2>(full_bar(stage), phase, abort_word, kWhoMma)) {
             alive = false;
@@ -277,10 +284,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t sA = base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_BYTES;
 #pragma unroll
-          for (int k = 0; k < K_STEPS; ++k) {
-            const uint64_t ad = ptx::make_smem_desc(sA + k * a_adv, a_lbo, 1024u);
-            const uint64_t bd = ptx::make_smem_desc(sB + k * b_adv, b_lbo, 1024u);
-            ptx::umma<kCtaGroup, kTf32>(acc, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int h = 0; h < kNH; ++h) {
+#pragma unroll
+            for (int k = 0; k < K_STEPS; ++k) {
+              const uint64_t ad = ptx::make_smem_desc(sA + k * a_adv, a_lbo, 1024u);
+              const uint64_t bd = ptx::make_smem_desc(sB + h * BH_BYTES + k * b_adv, b_lbo, 1024u);
+              ptx::umma<kCtaGroup, kTf32>(acc + h * BNH, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           // Frees the stage (in both CTAs) once the MMAs above have read it.
           ptx::umma_commit<kCtaGroup>(empty_bar(stage));
@@ -298,43 +308,98 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue
+    const int ew = warp - 2;          // epilogue warp index
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
+    const int half = ew >> 2;         // which 256-column half of the tile this warp drains
     const int out_dt = p.out_dtype;
     const size_t out_es = (out_dt == B200S_FP32) ? 4 : 2;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && ((p.ldc * out_es) % 16 == 0) &&
                         ((p.strideC * out_es) % 16 == 0);
+    const uint32_t stg = staging_base + static_cast<uint32_t>(ew * STG_BUFS) * 4096u;
+    const uint32_t sw = static_cast<uint32_t>(lane & 7);
     int it = 0;
+    int stage_flip = 0;
     for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it) {
       int b, mt, nt;
       decode_tile(p, tile, b, mt, nt);
-      const int buf = it & 1;
-      const uint32_t aphase = (it >> 1) & 1u;
+      const int buf = it % ACC_BUFS;
+      const uint32_t aphase = (it / ACC_BUFS) & 1u;
       bool ok = ptx::mbar_wait<kCtaGroup == 2>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const int row = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM + lane_group * 32 + lane;
-      const int col0 = nt * BN;
+      const int row_warp = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM + lane_group * 32;
+      const int row = row_warp + lane;
+      const int col0 = nt * BN_TILE + half * BNH;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
-                             static_cast<uint32_t>(buf * BN);
-      uint8_t* crow = static_cast<uint8_t*>(p.C) +
-                      (static_cast<int64_t>(b) * p.strideC + static_cast<int64_t>(row) * p.ldc) * out_es;
+                             static_cast<uint32_t>(buf * BN_TILE + half * BNH);
+      if (p.tma_store) {
+        // 128-byte row groups: tcgen05.ld -> convert -> swizzled st.shared -> one TMA store of a
+        // 32-row x 128-byte box per group.
+        const int cols_per_group = out_es == 4 ? 32 : 64;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, r);
-        ptx::tmem_ld_wait();
-        const int col = col0 + c * 32;
-        const int ncols = min(32, p.N - col);
-        if (row < p.M && ncols > 0) {
-          if (out_dt == B200S_BF16)
-            store_row32(reinterpret_cast<__nv_bfloat16*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
-          else if (out_dt == B200S_FP16)
-            store_row32(reinterpret_cast<__half*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
-          else
-            store_row32(reinterpret_cast<float*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+        for (int gc = 0; gc < BNH; gc += cols_per_group) {
+          const uint32_t sbuf = stg + static_cast<uint32_t>(stage_flip) * 4096u;
+          const uint32_t srow = sbuf + static_cast<uint32_t>(lane) * 128u;
+          uint32_t h[32];
+          if (out_es == 4) {
+            ptx::tmem_ld_32x32(taddr + gc, h);
+            ptx::tmem_ld_wait();
+          } else {
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld_32x32(taddr + gc, r0);
+            ptx::tmem_ld_32x32(taddr + gc + 32, r1);
+            ptx::tmem_ld_wait();
+            if (out_dt == B200S_BF16) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                h[j] = ptx::pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                h[16 + j] = ptx::pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                h[j] = ptx::pack_f16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                h[16 + j] = ptx::pack_f16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+              }
+            }
+          }
+          // the store that last read this staging buffer must be done with it
+          if (lane == 0) ptx::tma_store_wait_read<STG_BUFS - 1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            ptx::st_shared_v4(srow + ((static_cast<uint32_t>(j) ^ sw) << 4), h[4 * j], h[4 * j + 1], h[4 * j + 2],
+                              h[4 * j + 3]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_3d(&tmC, sbuf, col0 + gc, row_warp, b);
+            ptx::tma_store_commit();
+          }
+          if constexpr (STG_BUFS == 2) stage_flip ^= 1;
+        }
+      } else {
+        uint8_t* crow = static_cast<uint8_t*>(p.C) +
+                        (static_cast<int64_t>(b) * p.strideC + static_cast<int64_t>(row) * p.ldc) * out_es;
+#pragma unroll 1
+        for (int c = 0; c < BNH / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          const int col = col0 + c * 32;
+          const int ncols = min(32, p.N - col);
+          if (row < p.M && ncols > 0) {
+            if (out_dt == B200S_BF16)
+              store_row32(reinterpret_cast<__nv_bfloat16*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+            else if (out_dt == B200S_FP16)
+              store_row32(reinterpret_cast<__half*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+            else
+              store_row32(reinterpret_cast<float*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
+          }
         }
       }
+      // All tcgen05.ld of this warp have completed: hand the accumulator back.
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -344,6 +409,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           ptx::mbar_arrive(tempty_bar(buf));
       }
     }
+    if (p.tma_store && lane == 0) ptx::tma_store_wait_all<0>();  // shared memory must outlive the stores
+    __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
@@ -389,7 +456,7 @@ EncodeTiledFn encode_fn() {
 // Tensor map over an operand stored as [batch][rows][cols], cols contiguous, with a box of
 // box_rows x (128 bytes of cols) and the 128-byte swizzle.
 int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int64_t ld,
-                     int64_t batch, int64_t batch_stride, int box_rows) {
+                     int64_t batch, int64_t batch_stride, int box_rows, bool for_store = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return B200S_ERR_CUDA;
   const size_t es = dtype_size(dtype);
@@ -404,7 +471,7 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows,
   cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / es), static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_SWIZZLE_128B, for_store ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     note_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -413,13 +480,25 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows,
   return B200S_OK;
 }
 
-template <int kCtaGroup, int BN, int kStages, bool kTf32>
-int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmKernelParams kp, cudaStream_t stream) {
-  constexpr int BN_CTA = BN / kCtaGroup;
-  constexpr int STAGE_BYTES = kBM * kRowBytes + BN_CTA * kRowBytes;
-  constexpr int SMEM = kStages * STAGE_BYTES + 8 * (2 * kStages + 4) + 16 + 1024;
+// m-tiles per raster group: 8 unless B200S_RASTER_GROUP overrides it (tuning experiments).
+int raster_group_setting() {
+  static int value = [] {
+    const char* e = std::getenv("B200S_RASTER_GROUP");
+    int v = e ? std::atoi(e) : 8;
+    return v >= 1 && v <= 64 ? v : 8;
+  }();
+  return value;
+}
+
+template <int kCtaGroup, int kNH, int kStages, bool kTf32>
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmKernelParams kp,
+                   cudaStream_t stream) {
+  constexpr int kThreadsV = 64 + 128 * kNH;
+  constexpr int STAGE_BYTES = kBM * kRowBytes + kNH * (256 / kCtaGroup) * kRowBytes;
+  constexpr int STAGING_BYTES = 4 * kNH * (kNH == 1 ? 2 : 1) * 4096;
+  constexpr int SMEM = kStages * STAGE_BYTES + STAGING_BYTES + 8 * (2 * kStages + 4) + 16 + 1024;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
-  auto kernel = gemm_kernel<kCtaGroup, BN, kStages, kTf32>;
+  auto kernel = gemm_kernel<kCtaGroup, kNH, kStages, kTf32>;
 
   // Per-device one-time setup: opt in to the shared-memory size and find out how many
   // clusters can be resident at once (static tile striding needs all of them co-resident).
@@ -437,7 +516,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmKernelPar
       if (kCtaGroup == 2) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(sm_count() / 2 * 2);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(kThreadsV);
         cfg.dynamicSmemBytes = SMEM;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -459,7 +538,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmKernelPar
   const int clusters = kp.total_tiles < resident ? kp.total_tiles : resident;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(clusters * kCtaGroup);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreadsV);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];
@@ -469,7 +548,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmKernelPar
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  B200S_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, kp));
+  B200S_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, kp));
   count_launch();
   return B200S_OK;
 }
@@ -489,9 +568,13 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   uint32_t* status = device_status_words();
   if (!status) return B200S_ERR_CUDA;
 
-  int cta_group = g.cta_group;
-  if (cta_group == 0) cta_group = 2;
-  const int BN = 256;
+  // Tile variant: 1 = one CTA, 128 x 256 tiles; 2 = CTA pair, 256 x 256 tiles, double-buffered
+  // accumulators; 3 = CTA pair, 256 x 512 tiles. Wide outputs default to 3, narrow ones to 2.
+  int variant = g.cta_group;
+  if (variant == 0) variant = (g.N >= 1024 && g.M >= 256) ? 3 : 2;
+  const int cta_group = variant == 1 ? 1 : 2;
+  const int nh = variant == 3 ? 2 : 1;
+  const int BN = 256 * nh;
   const int bke = kRowBytes / static_cast<int>(es);
 
   CUtensorMap tmA, tmB;
@@ -502,14 +585,27 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   else
     rc = make_operand_map(&tmA, g.A, g.in_dtype, g.K, g.M, g.lda, g.batch, g.strideA, bke);
   if (rc) return rc;
-  const int bn_cta = BN / cta_group;
+  const int bn_cta = 256 / cta_group;  // rows of one B half this CTA loads
   if (g.b_major == B200S_K_MAJOR)
     rc = make_operand_map(&tmB, g.B, g.in_dtype, g.N, g.K, g.ldb, g.batch, g.strideB, bn_cta);
   else
     rc = make_operand_map(&tmB, g.B, g.in_dtype, g.K, g.N, g.ldb, g.batch, g.strideB, bke);
   if (rc) return rc;
 
+  // The epilogue stores through TMA when C can be described by a tensor map and is overwritten.
+  const size_t oes = dtype_size(g.out_dtype);
+  const bool tma_store = g.beta == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc * oes) % 16 == 0 &&
+                         (g.batch == 1 || (g.strideC * oes) % 16 == 0);
+  CUtensorMap tmC;
+  if (tma_store) {
+    rc = make_operand_map(&tmC, g.C, g.out_dtype, g.M, g.N, g.ldc, g.batch, g.strideC, 32, true);
+    if (rc) return rc;
+  } else {
+    tmC = tmA;  // never dereferenced
+  }
+
   GemmKernelParams kp;
+  kp.tma_store = tma_store ? 1 : 0;
   kp.M = static_cast<int32_t>(g.M);
   kp.N = static_cast<int32_t>(g.N);
   const int tile_m = kBM * cta_group;
@@ -519,6 +615,7 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles * g.batch;
   if (total > INT32_MAX) return B200S_ERR_BAD_SHAPE;
   kp.total_tiles = static_cast<int32_t>(total);
+  kp.raster_group = raster_group_setting();
   kp.a_mn = g.a_major == B200S_MN_MAJOR;
   kp.b_mn = g.b_major == B200S_MN_MAJOR;
   kp.fmt = tf32 ? 2 : (g.in_dtype == B200S_BF16 ? 1 : 0);
@@ -529,12 +626,16 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   kp.C = g.C;
   kp.status = status;
 
-  if (cta_group == 2) {
-    if (tf32) return launch_variant<2, 256, 6, true>(tmA, tmB, kp, stream);
-    return launch_variant<2, 256, 6, false>(tmA, tmB, kp, stream);
+  if (variant == 3) {
+    if (tf32) return launch_variant<2, 2, 4, true>(tmA, tmB, tmC, kp, stream);
+    return launch_variant<2, 2, 4, false>(tmA, tmB, tmC, kp, stream);
   }
-  if (tf32) return launch_variant<1, 256, 4, true>(tmA, tmB, kp, stream);
-  return launch_variant<1, 256, 4, false>(tmA, tmB, kp, stream);
+  if (variant == 2) {
+    if (tf32) return launch_variant<2, 1, 6, true>(tmA, tmB, tmC, kp, stream);
+    return launch_variant<2, 1, 6, false>(tmA, tmB, tmC, kp, stream);
+  }
+  if (tf32) return launch_variant<1, 1, 4, true>(tmA, tmB, tmC, kp, stream);
+  return launch_variant<1, 1, 4, false>(tmA, tmB, tmC, kp, stream);
 }
 
 }  // namespace b200s

@@ -193,6 +193,119 @@ int launch_side(const PreaddArgs& a, cudaStream_t stream) {
                      : launch_dtype<DEPTH, ALGO, sched::kSideB>(a, stream);
 }
 
+// ---- outer-group form ----------------------------------------------------------------------
+// One launch forms the operand blocks of a few outer products p1 only (7 blocks each at two
+// levels, 1 at one level), so the pipelined driver can start the products of the first group
+// while the later groups' operands are still being formed. The outer row of the table is a
+// run-time argument; the inner level stays compile-time.
+
+struct PreaddOuterParams {
+  const void* X;
+  void* out;
+  int64_t rows_blk, cols_vec;  // finest block rows, 16-byte vectors per finest block row
+  int64_t ld, strideX;
+  int64_t out_batch_blocks;    // blocks per batch item in `out` (7^depth)
+  int32_t transposed;
+  int8_t coef[7][4];           // [listed group][outer quadrant]
+  int32_t out_block0[7];       // first output block of each listed group
+};
+
+template <int INNER, int ALGO, int SIDE, typename T>
+__global__ void __launch_bounds__(256, 3) preadd_outer_kernel(const PreaddOuterParams p) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int NQ2 = INNER ? 4 : 1;
+  constexpr int NP2 = INNER ? 7 : 1;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.rows_blk * p.cols_vec) return;
+  const int64_t row = idx / p.cols_vec;
+  const int64_t cv = idx - row * p.cols_vec;
+  const int64_t cols_blk = p.cols_vec * VEC;
+  const int g = blockIdx.y;
+  const T* X = static_cast<const T*>(p.X) + static_cast<int64_t>(blockIdx.z) * p.strideX;
+
+  float t[NQ2][VEC];
+#pragma unroll
+  for (int q2 = 0; q2 < NQ2; ++q2) {
+    bool first = true;
+#pragma unroll
+    for (int q1 = 0; q1 < 4; ++q1) {
+      const int c = p.coef[g][q1];
+      if (c != 0) {
+        // position of (outer q1, inner q2) in the block grid, in storage orientation
+        const int lr = INNER ? 2 * (q1 >> 1) + (q2 >> 1) : (q1 >> 1);
+        const int lc = INNER ? 2 * (q1 & 1) + (q2 & 1) : (q1 & 1);
+        const int sr = p.transposed ? lc : lr;
+        const int sc = p.transposed ? lr : lc;
+        float x[VEC];
+        load_vec<T>(X + (sr * p.rows_blk + row) * p.ld + sc * cols_blk + cv * VEC, x);
+        if (first) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) t[q2][i] = c > 0 ? x[i] : -x[i];
+          first = false;
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) t[q2][i] = c > 0 ? t[q2][i] + x[i] : t[q2][i] - x[i];
+        }
+      }
+    }
+  }
+  const int64_t blk_elems = p.rows_blk * cols_blk;
+  T* out = static_cast<T*>(p.out) +
+           (static_cast<int64_t>(blockIdx.z) * p.out_batch_blocks + p.out_block0[g]) * blk_elems + row * cols_blk +
+           cv * VEC;
+  if constexpr (INNER) {
+    // the inner level: the same compile-time table walk as the single-pass kernel at depth 1
+    Preadd<1, ALGO, SIDE, T>::all_products(t, out, blk_elems, std::make_integer_sequence<int, NP2>{});
+  } else {
+    store_vec<T>(out, t[0]);
+  }
+}
+
+template <int INNER, int ALGO, int SIDE, typename T>
+int launch_outer_one(const PreaddOuterArgs& a, cudaStream_t stream) {
+  constexpr int VEC = Vec16<T>::N;
+  PreaddOuterParams kp;
+  kp.X = a.X;
+  kp.out = a.out;
+  kp.rows_blk = a.rows_blk;
+  kp.cols_vec = a.cols_blk / VEC;
+  kp.ld = a.ld;
+  kp.strideX = a.strideX;
+  kp.out_batch_blocks = sched::ipow(7, INNER + 1);
+  kp.transposed = a.transposed;
+  for (int g = 0; g < a.n_groups; ++g) {
+    for (int q = 0; q < 4; ++q) kp.coef[g][q] = static_cast<int8_t>(sched::uv1(ALGO, SIDE, a.groups[g], q));
+    kp.out_block0[g] = a.out_block0[g];
+  }
+  const int64_t total = kp.rows_blk * kp.cols_vec;
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.n_groups), static_cast<unsigned>(a.batch));
+  preadd_outer_kernel<INNER, ALGO, SIDE, T><<<grid, 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
+
+template <int INNER, int ALGO, int SIDE>
+int launch_outer_dtype(const PreaddOuterArgs& a, cudaStream_t stream) {
+  switch (a.dtype) {
+    case B200S_BF16:
+      return launch_outer_one<INNER, ALGO, SIDE, __nv_bfloat16>(a, stream);
+    case B200S_FP16:
+      return launch_outer_one<INNER, ALGO, SIDE, __half>(a, stream);
+    case B200S_FP32:
+      return launch_outer_one<INNER, ALGO, SIDE, float>(a, stream);
+  }
+  return B200S_ERR_BAD_DTYPE;
+}
+
+template <int INNER, int ALGO>
+int launch_outer_side(const PreaddOuterArgs& a, cudaStream_t stream) {
+  return a.side == 0 ? launch_outer_dtype<INNER, ALGO, sched::kSideA>(a, stream)
+                     : launch_outer_dtype<INNER, ALGO, sched::kSideB>(a, stream);
+}
+
 }  // namespace
 
 int launch_preadd(const PreaddArgs& a, cudaStream_t stream) {
@@ -209,6 +322,28 @@ int launch_preadd(const PreaddArgs& a, cudaStream_t stream) {
     return wino ? launch_side<1, sched::kWinograd>(a, stream) : launch_side<1, sched::kClassic>(a, stream);
   if (a.depth == 2)
     return wino ? launch_side<2, sched::kWinograd>(a, stream) : launch_side<2, sched::kClassic>(a, stream);
+  return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s
+
+namespace b200s {
+
+int launch_preadd_outer(const PreaddOuterArgs& a, cudaStream_t stream) {
+  const size_t es = dtype_size(a.dtype);
+  const int vec = static_cast<int>(16 / es);
+  if (a.rows_blk <= 0 || a.cols_blk <= 0 || a.batch <= 0 || a.n_groups <= 0 || a.n_groups > 7)
+    return B200S_ERR_BAD_SHAPE;
+  if (a.cols_blk % vec) return B200S_ERR_BAD_SHAPE;
+  if ((a.ld * es) % 16 || (a.batch > 1 && (a.strideX * es) % 16)) return B200S_ERR_BAD_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(a.X) & 15u) || (reinterpret_cast<uintptr_t>(a.out) & 15u))
+    return B200S_ERR_BAD_ALIGNMENT;
+  const bool wino = a.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && a.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (a.depth == 1)
+    return wino ? launch_outer_side<0, sched::kWinograd>(a, stream) : launch_outer_side<0, sched::kClassic>(a, stream);
+  if (a.depth == 2)
+    return wino ? launch_outer_side<1, sched::kWinograd>(a, stream) : launch_outer_side<1, sched::kClassic>(a, stream);
   return B200S_ERR_BAD_DEPTH;
 }
 

@@ -46,7 +46,7 @@ def status_ok(ops):
 EDGE = [127, 128, 129, 257, 300]
 
 
-@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("tile_variant", [1, 2, 3])
 @pytest.mark.parametrize("M", EDGE)
 @pytest.mark.parametrize("N", [256, 264, 520])
 def test_dense_tile_edges(ops, tile_variant, M, N):
@@ -60,7 +60,7 @@ def test_dense_tile_edges(ops, tile_variant, M, N):
     status_ok(ops)
 
 
-@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("tile_variant", [1, 2, 3])
 @pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_dense_operand_majors(ops, tile_variant, a_t, b_t, dtype):
@@ -102,7 +102,7 @@ def test_dense_batched_and_beta(ops):
 
 # ------------------------------------------------------------------ Strassen vs the oracle
 
-@pytest.mark.parametrize("tile_variant", [1, 2])
+@pytest.mark.parametrize("tile_variant", [1, 2, 3])
 @pytest.mark.parametrize("algo", ["classic", "winograd"])
 @pytest.mark.parametrize("depth", [1, 2])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -172,7 +172,35 @@ def test_against_committed_reference_outputs(ops, case):
     e_gpu = so.errors_vs_fp64(got, A, B)[1]
     floor = 2e-3 if got.dtype == torch.float32 else 0.0   # fp32 inputs run as TF32 on the tensor cores
     assert rel(got, want) <= 1.5 * (e_ref + e_gpu) + floor
-    assert e_gpu <= max(1.3 * e_ref, floor), (e_gpu, e_ref)
+    # As shipped, the fp32-agg function runs every level below the top in fp32
+    # (fixed_strassen_fp32_agg.py:99-113 drops base_dtype), so at depth >= 2 its error is that of a
+    # one-level scheme; the bar there is the same function with base_dtype forwarded.
+    bar = e_ref
+    if mod == "fixed_strassen_fp32_agg" and depth >= 2 and base is not None:
+        bar = max(bar, so.errors_vs_fp64(so.n_layers(A.to(base), B.to(base), depth, base, True, True), A, B)[1])
+    assert e_gpu <= max(1.3 * bar, floor), (e_gpu, e_ref, bar)
+    status_ok(ops)
+
+
+@pytest.mark.parametrize("algo", ["classic", "winograd"])
+@pytest.mark.parametrize("depth", [1, 2])
+@pytest.mark.parametrize("beta", [0, 1])
+def test_pipelined_driver_matches_sequential(ops, algo, depth, beta):
+    """The three-stream pipelined schedule and the single-stream one compute the same sums; only
+    the grouping of the fp32 recombination differs."""
+    M, N, K = 768, 512, 1024
+    A, B = seeded_pair(21, (M, K), (K, N), dist="uniform")
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    C0 = torch.randn(M, N, device="cuda").bfloat16()
+    Cs, Cp = C0.clone(), C0.clone()
+    ops.matmul_out(A, B, Cs, algo=algo, depth=depth, beta=beta, pipeline=2)
+    ops.matmul_out(A, B, Cp, algo=algo, depth=depth, beta=beta, pipeline=1)
+    ops.matmul_out(A, B, Cp.clone(), algo=algo, depth=depth, beta=0, pipeline=1)   # back-to-back reuse of the streams
+    assert rel(Cp, Cs) < 2e-4
+    want = so.library_model(A.cpu(), B.cpu(), depth, algo, out_dtype=torch.float32)
+    if beta:
+        want = want + C0.cpu().float()      # C += A.B: one rounding, after the addition
+    assert rel(Cp.cpu(), want.bfloat16()) < 1.5e-3
     status_ok(ops)
 
 
