@@ -324,8 +324,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       decode_tile(p, tile, b, mt, nt);
       const int buf = it % ACC_BUFS;
       const uint32_t aphase = (it / ACC_BUFS) & 1u;
-      bool ok = ptx::mbar_wait<kCtaGroup == 2>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue);
-      ok = __all_sync(0xffffffffu, ok);
+      // one lane waits, the warp follows
+      int ok = 1;
+      if (lane == 0) ok = ptx::mbar_wait<kCtaGroup == 2>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const int row_warp = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM + lane_group * 32;
