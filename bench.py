@@ -38,8 +38,8 @@ METRIC = "effective TFLOP/s (2MNK/t) bf16 Strassen"
 UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) of one launch of the grouped GEMM kernel on the N=1 workload, from
-# the ncu launch list summarised in profiles/gemm_grouped_16384_depth2.md.
-GEMM_DRAM_TRAFFIC_BYTES = 12.8e9
+# the ncu launch list summarised in profiles/bench_16384_depth2_launch_list.md.
+GEMM_DRAM_TRAFFIC_BYTES = 7.40e9
 
 
 def measured_peaks():

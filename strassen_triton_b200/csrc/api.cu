@@ -465,7 +465,7 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
 
   // Large single products run the pipelined driver unless the caller chose otherwise.
   const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
-  const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 4096.0 * 4096.0 * 4096.0);
+  const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 24576.0 * 24576.0 * 24576.0);
   if (p->batch == 1 && pipelined) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 
   rc = b200s_preadd(p, 0, A, Sa, stream_v);

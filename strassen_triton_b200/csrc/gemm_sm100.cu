@@ -263,6 +263,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t a_lbo = p.a_mn ? CHUNK_BYTES : 16u, b_lbo = p.b_mn ? CHUNK_BYTES : 16u;
       const uint32_t a_adv = p.a_mn ? (UMMA_K / 8) * 1024u : 32u;
       const uint32_t b_adv = p.b_mn ? (UMMA_K / 8) * 1024u : 32u;
+      const uint64_t a_desc0 = ptx::make_smem_desc(base, a_lbo, 1024u);
+      const uint64_t b_desc0 = ptx::make_smem_desc(base + A_BYTES, b_lbo, 1024u);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool alive = true;
@@ -281,15 +283,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t sA = base + stage * STAGE_BYTES;
-          const uint32_t sB = sA + A_BYTES;
+          // descriptors differ from the stage-0 ones only in the (16-byte granular) start address
+          const uint32_t soff = stage * (STAGE_BYTES >> 4);
+          const uint32_t accf = kb != 0 ? 1u : 0u;
 #pragma unroll
           for (int h = 0; h < kNH; ++h) {
 #pragma unroll
             for (int k = 0; k < K_STEPS; ++k) {
-              const uint64_t ad = ptx::make_smem_desc(sA + k * a_adv, a_lbo, 1024u);
-              const uint64_t bd = ptx::make_smem_desc(sB + h * BH_BYTES + k * b_adv, b_lbo, 1024u);
-              ptx::umma<kCtaGroup, kTf32>(acc + h * BNH, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              const uint64_t ad = a_desc0 + (soff + k * (a_adv >> 4));
+              const uint64_t bd = b_desc0 + (soff + h * (BH_BYTES >> 4) + k * (b_adv >> 4));
+              ptx::umma<kCtaGroup, kTf32>(acc + h * BNH, ad, bd, idesc, k == 0 ? accf : 1u);
             }
           }
           // Frees the stage (in both CTAs) once the MMAs above have read it.
@@ -326,7 +329,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t aphase = (it / ACC_BUFS) & 1u;
       // one lane waits, the warp follows
       int ok = 1;
-      if (lane == 0) ok = ptx::mbar_wait<kCtaGroup == 2>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue) ? 1 : 0;
+      if (lane == 0) ok = ptx::mbar_wait<kCtaGroup == 2, 64>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       ptx::tc_fence_after_sync();

@@ -92,11 +92,50 @@ __device__ __forceinline__ void store_vec<__half>(__half* ptr, const float (&f)[
   *reinterpret_cast<uint4*>(ptr) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-template <int DEPTH, int ALGO, int SIDE, typename T>
+// 8-byte forms for four 16-bit elements: the depth-2 single-pass kernel holds 16 x 4 inputs
+// instead of 16 x 8, so three times as many threads are resident and keep loads in flight.
+__device__ __forceinline__ void load_vec4(const __nv_bfloat16* ptr, float (&f)[4]) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(ptr));
+  f[0] = __uint_as_float(v.x << 16), f[1] = __uint_as_float(v.x & 0xffff0000u);
+  f[2] = __uint_as_float(v.y << 16), f[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+__device__ __forceinline__ void load_vec4(const __half* ptr, float (&f)[4]) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(ptr));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
+__device__ __forceinline__ void load_vec4(const float* ptr, float (&f)[4]) { load_vec<float>(ptr, f); }
+__device__ __forceinline__ void store_vec4(__nv_bfloat16* ptr, const float (&f)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(ptr) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+__device__ __forceinline__ void store_vec4(__half* ptr, const float (&f)[4]) {
+  const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(ptr) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+__device__ __forceinline__ void store_vec4(float* ptr, const float (&f)[4]) { store_vec<float>(ptr, f); }
+
+template <typename T, int N>
+__device__ __forceinline__ void load_n(const T* ptr, float (&f)[N]) {
+  if constexpr (N == Vec16<T>::N)
+    load_vec<T>(ptr, f);
+  else
+    load_vec4(ptr, f);
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_n(T* ptr, const float (&f)[N]) {
+  if constexpr (N == Vec16<T>::N)
+    store_vec<T>(ptr, f);
+  else
+    store_vec4(ptr, f);
+}
+
+template <int DEPTH, int ALGO, int SIDE, typename T, int VEC_ = Vec16<T>::N>
 struct Preadd {
   static constexpr int NQ = sched::ipow(4, DEPTH);
   static constexpr int NP = sched::ipow(7, DEPTH);
-  static constexpr int VEC = Vec16<T>::N;
+  static constexpr int VEC = VEC_;
 
   template <int P, int Q>
   static __device__ __forceinline__ void add_term(const float (&x)[NQ][VEC], float (&acc)[VEC], bool& first) {
@@ -119,7 +158,7 @@ struct Preadd {
     float acc[VEC];
     bool first = true;
     (add_term<P, Qs>(x, acc, first), ...);
-    store_vec<T>(out_blk0 + P * blk_elems, acc);
+    store_n<T, VEC>(out_blk0 + P * blk_elems, acc);
   }
 
   template <int... Ps>
@@ -129,9 +168,14 @@ struct Preadd {
   }
 };
 
+template <int DEPTH, typename T>
+struct PreaddVec {
+  static constexpr int N = DEPTH == 2 ? 4 : Vec16<T>::N;
+};
+
 template <int DEPTH, int ALGO, int SIDE, typename T>
-__global__ void __launch_bounds__(256) preadd_kernel(const PreaddKernelParams p) {
-  using PA = Preadd<DEPTH, ALGO, SIDE, T>;
+__global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 1) preadd_kernel(const PreaddKernelParams p) {
+  using PA = Preadd<DEPTH, ALGO, SIDE, T, PreaddVec<DEPTH, T>::N>;
   constexpr int NQ = PA::NQ, NP = PA::NP, VEC = PA::VEC;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= p.rows_blk * p.cols_vec) return;
@@ -146,7 +190,7 @@ __global__ void __launch_bounds__(256) preadd_kernel(const PreaddKernelParams p)
     const int lr = sched::block_row(DEPTH, q), lc = sched::block_col(DEPTH, q);
     const int sr = p.transposed ? lc : lr;
     const int sc = p.transposed ? lr : lc;
-    load_vec<T>(X + (sr * p.rows_blk + row) * p.ld + sc * cols_blk + cv * VEC, x[q]);
+    load_n<T, VEC>(X + (sr * p.rows_blk + row) * p.ld + sc * cols_blk + cv * VEC, x[q]);
   }
   const int64_t blk_elems = p.rows_blk * cols_blk;
   T* out = static_cast<T*>(p.out) + static_cast<int64_t>(blockIdx.y) * NP * blk_elems + row * cols_blk + cv * VEC;
@@ -155,7 +199,7 @@ __global__ void __launch_bounds__(256) preadd_kernel(const PreaddKernelParams p)
 
 template <int DEPTH, int ALGO, int SIDE, typename T>
 int launch_one(const PreaddArgs& a, cudaStream_t stream) {
-  constexpr int VEC = Vec16<T>::N;
+  constexpr int VEC = PreaddVec<DEPTH, T>::N;
   PreaddKernelParams kp;
   kp.X = a.X;
   kp.out = a.out;

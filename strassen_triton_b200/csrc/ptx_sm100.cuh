@@ -100,13 +100,15 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Waits for the phase with the given parity. Returns false (and sets *abort_word,
 // a word in shared memory that all roles of the CTA poll) when the limit runs out
 // or when another role has already given up.
-template <bool kClusterScope = false>
+// kBackoffNs > 0 sleeps that long between polls: for waits that normally last a whole main loop.
+template <bool kClusterScope = false, int kBackoffNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_word, uint32_t who) {
   uint64_t start = 0;
   for (uint32_t it = 0;; ++it) {
     bool ok = kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
     if (ok) return true;
+    if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     if ((it & 0xffu) == 0xffu) {
       if (*abort_word != 0) return false;
       uint64_t now = global_timer_ns();
