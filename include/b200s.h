@@ -90,7 +90,9 @@ typedef struct b200s_problem {
   int32_t pipeline;   /* how the Strassen passes are scheduled: 0 = library decides, 1 = pipelined
                          (operand sums and recombination run on side streams beside the products,
                          outer group by outer group), 2 = sequential on the caller's stream */
-  int32_t reserved;
+  int32_t b_blocks_ready; /* 1: the operand blocks of B already sit in `workspace` from an earlier call with
+                         the same B, extents, dtype, algo, depth and schedule (and the same workspace):
+                         skip forming them. Used when one B multiplies several row panels of A. */
 } b200s_problem;
 
 /* Library version, major*10000 + minor*100 + patch. */

@@ -119,6 +119,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   if (p->depth < -1 || p->depth > 2) return B200S_ERR_BAD_DEPTH;
   if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
   if (p->pipeline < 0 || p->pipeline > 2) return B200S_ERR_BAD_SHAPE;
+  if (p->b_blocks_ready != 0 && p->b_blocks_ready != 1) return B200S_ERR_BAD_SHAPE;
   const int64_t a_cols = p->a_major == B200S_K_MAJOR ? p->K : p->M;
   const int64_t b_cols = p->b_major == B200S_K_MAJOR ? p->K : p->N;
   if (p->lda < a_cols || p->ldb < b_cols || p->ldc < p->N) return B200S_ERR_BAD_STRIDE;
@@ -234,11 +235,13 @@ int run_pipelined(const b200s_problem* p, const Plan& plan, const void* A, const
     pa.ld = p->lda, pa.strideX = 0, pa.transposed = !a_k;
     rc = launch_preadd_outer(pa, ds->s_add);
     if (rc) return rc;
-    pa.X = B, pa.out = Sb, pa.side = 1;
-    pa.rows_blk = b_k ? plan.Nb : plan.Kb, pa.cols_blk = b_k ? plan.Kb : plan.Nb;
-    pa.ld = p->ldb, pa.transposed = b_k;
-    rc = launch_preadd_outer(pa, ds->s_add);
-    if (rc) return rc;
+    if (!p->b_blocks_ready) {
+      pa.X = B, pa.out = Sb, pa.side = 1;
+      pa.rows_blk = b_k ? plan.Nb : plan.Kb, pa.cols_blk = b_k ? plan.Kb : plan.Nb;
+      pa.ld = p->ldb, pa.transposed = b_k;
+      rc = launch_preadd_outer(pa, ds->s_add);
+      if (rc) return rc;
+    }
     B200S_CUDA_OK(cudaEventRecord(ds->ev_pre[i], ds->s_add));
   }
 
@@ -434,7 +437,10 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
     A = At;
     p->a_major = B200S_K_MAJOR, p->lda = p->K, p->strideA = p->M * p->K;
   }
-  if (plan.tb_bytes) {
+  const bool b_reused = p->b_blocks_ready && plan.depth > 0;
+  if (plan.tb_bytes && b_reused) {
+    p->b_major = B200S_K_MAJOR, p->ldb = p->K, p->strideB = p->K * p->N;  // blocks were formed from the K-major copy
+  } else if (plan.tb_bytes) {
     // fp32 B given K x N: rewrite it N x K
     void* Bt = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes + plan.ta_bytes;
     rc = launch_transpose_f32(B, Bt, p->K, p->N, p->ldb, p->K, p->batch, p->strideB, p->K * p->N, stream);
@@ -470,8 +476,10 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
 
   rc = b200s_preadd(p, 0, A, Sa, stream_v);
   if (rc) return rc;
-  rc = b200s_preadd(p, 1, B, Sb, stream_v);
-  if (rc) return rc;
+  if (!p->b_blocks_ready) {
+    rc = b200s_preadd(p, 1, B, Sb, stream_v);
+    if (rc) return rc;
+  }
 
   const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
   g.A = Sa, g.B = Sb, g.C = Mp;

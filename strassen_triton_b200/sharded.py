@@ -46,7 +46,20 @@ def sharded_matmul(A_block: torch.Tensor, B: torch.Tensor, M: int, *, group=None
     if matmul_fn is None:
         from . import ops
 
-        matmul_fn = lambda a, b: ops.matmul(a, b, **matmul_kwargs)  # noqa: E731
+        # One scratch buffer for all panels: B's operand blocks are formed by the first panel and
+        # reused by the later ones of the same extent (b_blocks_ready).
+        state = {"rows": None, "ws": matmul_kwargs.pop("workspace", None)}
+
+        def matmul_fn(a, b):
+            c = torch.empty((a.shape[0], b.shape[-1]), dtype=a.dtype, device=a.device)
+            p, _, _ = ops.make_problem(a, b, c, matmul_kwargs.get("algo", "auto"), matmul_kwargs.get("depth", -1))
+            need = ops.workspace_bytes(p)
+            if need and (state["ws"] is None or state["ws"].numel() < need):
+                state["ws"], state["rows"] = torch.empty(need, dtype=torch.uint8, device=a.device), None
+            ready = state["rows"] == a.shape[0] and need > 0
+            ops.matmul_out(a, b, c, b_blocks_ready=ready, workspace=state["ws"], **matmul_kwargs)
+            state["rows"] = a.shape[0]
+            return c
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     r0, r1 = row_block(M, world, rank)

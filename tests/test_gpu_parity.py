@@ -204,6 +204,28 @@ def test_pipelined_driver_matches_sequential(ops, algo, depth, beta):
     status_ok(ops)
 
 
+def test_b_blocks_are_reused_across_row_panels(ops):
+    """One B, several row panels of A, one workspace: the later panels skip B's operand sums."""
+    M, N, K = 1024, 512, 768
+    A, B = seeded_pair(33, (M, K), (K, N), dist="uniform")
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    want = torch.cat([ops.matmul(A[256 * i:256 * (i + 1)], B, algo="classic", depth=2) for i in range(4)])
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    p, _, _ = ops.make_problem(A[:256], B, C[:256], "classic", 2)
+    ws = torch.empty(ops.workspace_bytes(p), dtype=torch.uint8, device="cuda")
+    launches = []
+    from strassen_triton_b200 import _lib
+    for i in range(4):
+        n0 = _lib.load().b200s_launch_count()
+        ops.matmul_out(A[256 * i:256 * (i + 1)], B, C[256 * i:256 * (i + 1)], algo="classic", depth=2,
+                       b_blocks_ready=i > 0, workspace=ws)
+        launches.append(_lib.load().b200s_launch_count() - n0)
+    assert launches == [4, 3, 3, 3]
+    assert torch.equal(C, want)   # same arithmetic as four independent calls
+    assert rel(C, A.double() @ B.double()) < 2e-2
+    status_ok(ops)
+
+
 # ------------------------------------------------------------------ reference-named entry points
 
 def test_run_launchers_accumulate_and_return_none(ops):
