@@ -131,6 +131,35 @@ int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_dev
                  void* workspace_device, size_t workspace_bytes, void* stream);
 
 /*
+ * C (+)= A . B like b200s_matmul, for callers that cannot hand over scratch memory. (No counterpart
+ * in the reference: it is an addition of this library.)
+ *
+ * Who needs it: code that runs where device allocation is off the table - a real-time or
+ * safety-certified control loop that must not call an allocator after start-up, a plug-in hosted by
+ * an application that owns all device memory and gives its guests none, a callback that runs inside
+ * someone else's stream-ordered pipeline and may not synchronise or allocate. Such callers pass only
+ * the operands and the result; the blocks that b200s_matmul keeps in `workspace` live here in a
+ * fixed 64 MiB array that is part of the library image (so every GPU that loads the library carries
+ * those 64 MiB until the process exits). The function calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ *
+ * Limit: b200s_workspace_bytes(p) must not exceed 64 MiB (for bf16: depth 1 up to about 2048^3,
+ * depth 2 up to about 1792^3; any size at depth 0); larger problems return B200S_ERR_TOO_LARGE and
+ * launch nothing. Always the sequential schedule on `stream`; `pipeline` and `b_blocks_ready` are
+ * ignored.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and the
+ * device's properties; make that first call outside any stream capture. All calls share the one
+ * array: it still holds the previous call's blocks when a call starts, every byte a call reads it
+ * has written first, so nothing needs clearing - but two calls whose kernels can overlap on the GPU
+ * (different streams, or several host threads) overwrite each other's blocks and give wrong
+ * results. Serialise them on one stream. A wait that gives up inside this call is recorded in
+ * status words of the library image, not in those b200s_device_status reads.
+ */
+int b200s_matmul_static(const b200s_problem* p, const void* A_device, const void* B_device, void* C_device,
+                        void* stream);
+
+/*
  * The algorithm and depth b200s_matmul will use for p (resolves AUTO / -1 through the tuner
  * table; clamps depth to what the extents allow). Replaces the hand-chosen `depth=` arguments and
  * the triton.autotune config lists of strassen.py:9-30,93-114,218-236.

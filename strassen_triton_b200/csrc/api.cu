@@ -499,6 +499,131 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   return b200s_combine(p, Mp, C, stream_v);
 }
 
+// ---- product with built-in scratch ---------------------------------------------------------------
+//
+// Scratch for b200s_matmul_static lives in the library image instead of in memory the caller
+// allocates: a fixed array in device global memory, present on every GPU that loads the library for
+// as long as the process lives. In host code the array's name stands for the symbol, not for a
+// device address, so its address is asked from the runtime once per device (cudaGetSymbolAddress,
+// with that device current) and only that pointer is handed to kernels.
+constexpr size_t kStaticScratchBytes = size_t{64} << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) uint32_t g_static_status[2];  // zero at load; set only when a wait gives up
+
+namespace {
+struct StaticState {
+  bool ready = false;
+  void* scratch = nullptr;
+  uint32_t* status = nullptr;
+  int sms = 0;
+};
+std::mutex g_static_mu;
+StaticState g_static[64];
+
+// Set-up of the calling thread's current device: queries only, no allocation.
+int static_state(StaticState** out) {
+  int dev = -1;
+  B200S_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200S_ERR_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticState& s = g_static[dev];
+  if (!s.ready) {
+    int major = 0, sms = 0;
+    B200S_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    B200S_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (major != 10) return B200S_ERR_NO_DEVICE;
+    void* scratch = nullptr;
+    void* status = nullptr;
+    B200S_CUDA_OK(cudaGetSymbolAddress(&scratch, g_static_scratch));
+    B200S_CUDA_OK(cudaGetSymbolAddress(&status, g_static_status));
+    s.scratch = scratch;
+    s.status = static_cast<uint32_t*>(status);
+    s.sms = sms;
+    s.ready = true;
+  }
+  *out = &s;
+  return B200S_OK;
+}
+}  // namespace
+
+int b200s_matmul_static(const b200s_problem* p_in, const void* A, const void* B, void* C, void* stream_v) {
+  if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p_in, &plan);
+  if (rc) return rc;
+  if (plan.total_bytes > kStaticScratchBytes) return B200S_ERR_TOO_LARGE;
+  StaticState* st = nullptr;
+  rc = static_state(&st);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  b200s_problem local = *p_in;
+  b200s_problem* p = &local;
+  uint8_t* ws = static_cast<uint8_t*>(st->scratch);
+
+  // Same sequence as the sequential schedule of b200s_matmul, every pass on the caller's stream.
+  if (plan.ta_bytes) {
+    void* At = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes;
+    rc = launch_transpose_f32(A, At, p->K, p->M, p->lda, p->K, p->batch, p->strideA, p->M * p->K, stream);
+    if (rc) return rc;
+    A = At;
+    p->a_major = B200S_K_MAJOR, p->lda = p->K, p->strideA = p->M * p->K;
+  }
+  if (plan.tb_bytes) {
+    void* Bt = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes + plan.ta_bytes;
+    rc = launch_transpose_f32(B, Bt, p->K, p->N, p->ldb, p->K, p->batch, p->strideB, p->K * p->N, stream);
+    if (rc) return rc;
+    B = Bt;
+    p->b_major = B200S_K_MAJOR, p->ldb = p->K, p->strideB = p->K * p->N;
+  }
+  const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+
+  GemmArgs g;
+  g.status = st->status;
+  g.sms = st->sms;
+  g.cta_group = p->tile_variant;
+  if (g.cta_group < 0 || g.cta_group > 3) return B200S_ERR_BAD_SHAPE;
+  g.in_dtype = p->in_dtype, g.a_major = p->a_major, g.b_major = p->b_major;
+  if (plan.depth == 0) {
+    g.A = A, g.B = B, g.C = C;
+    g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
+    g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
+    g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
+    g.out_dtype = p->out_dtype, g.beta = p->beta;
+    return launch_gemm(g, stream);
+  }
+  void* Sa = ws;
+  void* Sb = ws + plan.sa_bytes;
+  void* Mp = ws + plan.sa_bytes + plan.sb_bytes;
+
+  PreaddArgs pa;
+  pa.batch = p->batch, pa.algo = plan.algo, pa.depth = plan.depth, pa.dtype = p->in_dtype;
+  pa.X = A, pa.out = Sa, pa.side = 0;
+  pa.rows_blk = a_k ? plan.Mb : plan.Kb, pa.cols_blk = a_k ? plan.Kb : plan.Mb;
+  pa.ld = p->lda, pa.strideX = p->strideA, pa.transposed = !a_k;
+  rc = launch_preadd(pa, stream);
+  if (rc) return rc;
+  pa.X = B, pa.out = Sb, pa.side = 1;
+  pa.rows_blk = b_k ? plan.Nb : plan.Kb, pa.cols_blk = b_k ? plan.Kb : plan.Nb;
+  pa.ld = p->ldb, pa.strideX = p->strideB, pa.transposed = b_k;
+  rc = launch_preadd(pa, stream);
+  if (rc) return rc;
+
+  g.A = Sa, g.B = Sb, g.C = Mp;
+  g.M = plan.Mb, g.N = plan.Nb, g.K = plan.Kb, g.batch = p->batch * plan.np;
+  g.lda = a_k ? plan.Kb : plan.Mb, g.ldb = b_k ? plan.Kb : plan.Nb, g.ldc = plan.Nb;
+  g.strideA = plan.Mb * plan.Kb, g.strideB = plan.Kb * plan.Nb, g.strideC = plan.Mb * plan.Nb;
+  g.out_dtype = plan.prod_dtype, g.beta = 0;
+  rc = launch_gemm(g, stream);
+  if (rc) return rc;
+
+  CombineArgs c;
+  c.products = Mp, c.C = C;
+  c.Mb = plan.Mb, c.Nb = plan.Nb, c.ldc = p->ldc, c.batch = p->batch, c.strideC = p->strideC;
+  c.algo = plan.algo, c.depth = plan.depth, c.prod_dtype = plan.prod_dtype, c.out_dtype = p->out_dtype;
+  c.beta = p->beta;
+  return launch_combine(c, stream);
+}
+
 int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out) {
   if (!status_out) return B200S_ERR_NULL_POINTER;
   uint32_t* words = device_status_words();

@@ -41,6 +41,10 @@ struct GemmArgs {
   int in_dtype, out_dtype;
   int beta;
   int cta_group;  // tile variant of b200s_problem: 0 = default, 1..3 = force
+  // Optional: device status words and SM count supplied by the caller instead of the per-device
+  // state of api.cu (nullptr / 0 = use that state).
+  uint32_t* status = nullptr;
+  int sms = 0;
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 

@@ -497,7 +497,7 @@ int raster_group_setting() {
 
 template <int kCtaGroup, int kNH, int kStages, bool kTf32>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmKernelParams kp,
-                   cudaStream_t stream) {
+                   int sms, cudaStream_t stream) {
   constexpr int kThreadsV = 64 + 128 * kNH;
   constexpr int STAGE_BYTES = kBM * kRowBytes + kNH * (256 / kCtaGroup) * kRowBytes;
   constexpr int STAGING_BYTES = 4 * kNH * (kNH == 1 ? 2 : 1) * 4096;
@@ -517,10 +517,10 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     if (dev < 0 || dev >= 64) return B200S_ERR_NO_DEVICE;
     if (max_clusters[dev] == 0) {
       B200S_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-      int n = sm_count() / kCtaGroup;
+      int n = sms / kCtaGroup;
       if (kCtaGroup == 2) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(sm_count() / 2 * 2);
+        cfg.gridDim = dim3(sms / 2 * 2);
         cfg.blockDim = dim3(kThreadsV);
         cfg.dynamicSmemBytes = SMEM;
         cudaLaunchAttribute at[1];
@@ -570,8 +570,10 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   if ((g.lda * es) % 16 || (g.ldb * es) % 16) return B200S_ERR_BAD_STRIDE;
   if (g.batch > 1 && ((g.strideA * es) % 16 || (g.strideB * es) % 16)) return B200S_ERR_BAD_STRIDE;
 
-  uint32_t* status = device_status_words();
+  uint32_t* status = g.status ? g.status : device_status_words();
   if (!status) return B200S_ERR_CUDA;
+  const int sms = g.sms > 0 ? g.sms : sm_count();
+  if (sms < 2) return B200S_ERR_NO_DEVICE;
 
   // Tile variant: 1 = one CTA, 128 x 256 tiles; 2 = CTA pair, 256 x 256 tiles, double-buffered
   // accumulators; 3 = CTA pair, 256 x 512 tiles. Wide outputs default to 3, narrow ones to 2.
@@ -632,15 +634,15 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   kp.status = status;
 
   if (variant == 3) {
-    if (tf32) return launch_variant<2, 2, 4, true>(tmA, tmB, tmC, kp, stream);
-    return launch_variant<2, 2, 4, false>(tmA, tmB, tmC, kp, stream);
+    if (tf32) return launch_variant<2, 2, 4, true>(tmA, tmB, tmC, kp, sms, stream);
+    return launch_variant<2, 2, 4, false>(tmA, tmB, tmC, kp, sms, stream);
   }
   if (variant == 2) {
-    if (tf32) return launch_variant<2, 1, 6, true>(tmA, tmB, tmC, kp, stream);
-    return launch_variant<2, 1, 6, false>(tmA, tmB, tmC, kp, stream);
+    if (tf32) return launch_variant<2, 1, 6, true>(tmA, tmB, tmC, kp, sms, stream);
+    return launch_variant<2, 1, 6, false>(tmA, tmB, tmC, kp, sms, stream);
   }
-  if (tf32) return launch_variant<1, 1, 4, true>(tmA, tmB, tmC, kp, stream);
-  return launch_variant<1, 1, 4, false>(tmA, tmB, tmC, kp, stream);
+  if (tf32) return launch_variant<1, 1, 4, true>(tmA, tmB, tmC, kp, sms, stream);
+  return launch_variant<1, 1, 4, false>(tmA, tmB, tmC, kp, sms, stream);
 }
 
 }  // namespace b200s
