@@ -285,8 +285,17 @@ def run_gpu_arm(args):
         C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         p, _, _ = ops.make_problem(A, B, C[r0:r1], "classic", depth)
         ws = torch.empty(ops.workspace_bytes(p), dtype=torch.uint8, device=dev)
-        step = lambda: sharded_matmul(A, B, n, panels=args.panels, out=C, algo="classic", depth=depth,  # noqa: E731
-                                      workspace=ws)
+        if args.exchange in ("peer", "peer_copy"):
+            from strassen_triton_b200.sharded import PeerShardedMatmul
+
+            del C, ws
+            plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo="classic", depth=depth, panels=args.panels,
+                                     device=dev, exchange="copy" if args.exchange == "peer_copy" else "store")
+            C = plan.C
+            step = lambda: plan(A, B)  # noqa: E731
+        else:
+            step = lambda: sharded_matmul(A, B, n, panels=args.panels, out=C, algo="classic", depth=depth,  # noqa: E731
+                                          workspace=ws)
         flops = 2.0 * n ** 3
 
     for _ in range(max(args.warmup, 3)):
@@ -327,7 +336,10 @@ def run_gpu_arm(args):
         def e2e_step():
             dA = hA.to(dev, non_blocking=True)
             dB = hB.to(dev, non_blocking=True)
-            out = sharded_matmul(dA, dB, n, panels=args.panels, out=C, algo="classic", depth=depth, workspace=ws)
+            if args.exchange in ("peer", "peer_copy"):
+                out = plan(dA, dB)
+            else:
+                out = sharded_matmul(dA, dB, n, panels=args.panels, out=C, algo="classic", depth=depth, workspace=ws)
             hC.copy_(out[r0:r1], non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
@@ -350,9 +362,13 @@ def run_gpu_arm(args):
             "config": workload_config(world), "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": "fixed_strassen_fp32_agg.strassen_matmul_n_layers" if world == 1
-                    else "strassen_triton_b200.sharded.sharded_matmul"},
+                    else ("strassen_triton_b200.sharded.PeerShardedMatmul" if args.exchange != "nccl"
+                          else "strassen_triton_b200.sharded.sharded_matmul")},
             "gpu_launches": int(launches),
         }
+        if world > 1:
+            line["config"]["exchange"] = args.exchange
+            line["config"]["panels"] = args.panels
         if world == 1:
             # per-kernel durations and the roofline of the dominant kernel (the grouped GEMM)
             stages = stage_breakdown(ops, _lib, A, B, C, depth, args.steps)
@@ -398,7 +414,10 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--panels", type=int, default=4, help="row panels per rank for gather/compute overlap (N > 1)")
+    ap.add_argument("--panels", type=int, default=2, help="row panels per rank for exchange/compute overlap (N > 1)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_copy", "nccl"],
+                    help="N > 1: 'peer' = recombination kernel stores into every rank's C over NVLink; "
+                         "'nccl' = all-gather of the row blocks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -200,6 +200,17 @@ int64_t b200s_launch_count(void);
 int b200s_preadd(const b200s_problem* p, int side, const void* X_device, void* out_device, void* stream);
 int b200s_combine(const b200s_problem* p, const void* products_device, void* C_device, void* stream);
 
+/*
+ * b200s_combine writing the finished M x N product to n_dst (1..8) destinations at once: C_list[i]
+ * is the device address of element (0,0) of the product inside destination i, all with leading
+ * dimension p->ldc. Destinations may be memory of other GPUs mapped into this process (peer or
+ * symmetric memory): the stores are plain global stores, so a row-sharded product lands in every
+ * GPU's copy of C without a separate all-gather. beta must be 0 and batch 1. The reference has no
+ * multi-GPU product; this carries the exchange step of its north-star row-sharded configuration.
+ */
+int b200s_combine_peers(const b200s_problem* p, const void* products_device, void* const* C_list, int n_dst,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -80,6 +80,8 @@ SIGNATURES = {
     "b200s_device_status": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int32), _P(ctypes.c_int32)]),
     "b200s_launch_count": (ctypes.c_int64, []),
     "b200s_preadd": (ctypes.c_int, [_P(Problem), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "b200s_combine_peers": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int,
+                                           ctypes.c_void_p]),
     "b200s_combine": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
 }
 

@@ -412,6 +412,22 @@ int b200s_combine(const b200s_problem* p, const void* products, void* C, void* s
   return launch_combine(c, static_cast<cudaStream_t>(stream));
 }
 
+int b200s_combine_peers(const b200s_problem* p, const void* products, void* const* C_list, int n_dst, void* stream) {
+  if (!p || !products || !C_list) return B200S_ERR_NULL_POINTER;
+  Plan plan;
+  int rc = make_plan(p, &plan);
+  if (rc) return rc;
+  if (plan.depth == 0) return B200S_ERR_BAD_DEPTH;
+  if (p->batch != 1 || p->beta != 0) return B200S_ERR_BAD_SHAPE;
+  CombineArgs c;
+  c.products = products, c.C = nullptr;
+  c.Mb = plan.Mb, c.Nb = plan.Nb, c.ldc = p->ldc, c.batch = 1, c.strideC = 0;
+  c.algo = plan.algo, c.depth = plan.depth, c.prod_dtype = plan.prod_dtype, c.out_dtype = p->out_dtype;
+  c.beta = 0;
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  return launch_combine_peers(c, C_list, n_dst, static_cast<cudaStream_t>(stream));
+}
+
 int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* workspace,
                  size_t workspace_bytes, void* stream_v) {
   if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;

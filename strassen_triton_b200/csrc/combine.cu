@@ -254,6 +254,91 @@ int launch_dtype(const CombineArgs& a, cudaStream_t stream) {
   return B200S_ERR_BAD_DTYPE;
 }
 
+// ---- recombination fused with the exchange of a row-sharded product ------------------------------
+// Same arithmetic as combine_kernel, but every output vector is stored to several destinations:
+// this GPU's copy of C and the copies of its peers, reached through peer-mapped pointers (plain
+// st.global over NVLink). The all-gather of a row-sharded product then costs no separate pass: the
+// finished rows leave the SM straight for every GPU's memory.
+struct CombinePeersParams {
+  const void* products;
+  void* dst[8];
+  int32_t n_dst;
+  int64_t Mb, nb_vec;
+  int64_t ldc;
+  int32_t out_dtype, vec_ok;
+};
+
+template <int DEPTH, int ALGO, typename TP>
+__global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 3) combine_peers_kernel(const CombinePeersParams p) {
+  using CB = Combine<DEPTH, ALGO, TP>;
+  constexpr int NQ = CB::NQ, NP = CB::NP, VEC = CB::VEC;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= p.Mb * p.nb_vec) return;
+  const int64_t row = idx / p.nb_vec;
+  const int64_t cv = idx - row * p.nb_vec;
+  const int64_t Nb = p.nb_vec * VEC;
+  const int64_t blk_elems = p.Mb * Nb;
+  float acc[NQ][VEC];
+#pragma unroll
+  for (int r = 0; r < NQ; ++r)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[r][i] = 0.f;
+  const TP* prod0 = static_cast<const TP*>(p.products) + row * Nb + cv * VEC;
+  CB::all_products(prod0, blk_elems, acc, std::make_integer_sequence<int, NP>{});
+#pragma unroll
+  for (int r = 0; r < NQ; ++r) {
+    const int64_t off = (sched::block_row(DEPTH, r) * p.Mb + row) * p.ldc + sched::block_col(DEPTH, r) * Nb + cv * VEC;
+#pragma unroll 1
+    for (int d = 0; d < p.n_dst; ++d) {
+      if (p.out_dtype == B200S_BF16)
+        store_out<__nv_bfloat16, VEC>(static_cast<__nv_bfloat16*>(p.dst[d]) + off, acc[r], false, p.vec_ok != 0);
+      else if (p.out_dtype == B200S_FP16)
+        store_out<__half, VEC>(static_cast<__half*>(p.dst[d]) + off, acc[r], false, p.vec_ok != 0);
+      else
+        store_out<float, VEC>(static_cast<float*>(p.dst[d]) + off, acc[r], false, p.vec_ok != 0);
+    }
+  }
+}
+
+template <int DEPTH, int ALGO, typename TP>
+int launch_peers_one(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream) {
+  constexpr int VEC = Combine<DEPTH, ALGO, TP>::VEC;
+  CombinePeersParams kp;
+  kp.products = a.products;
+  kp.n_dst = n_dst;
+  const size_t oes = dtype_size(a.out_dtype);
+  bool vec_ok = ((a.ldc * oes) % 16 == 0) && ((a.Nb * oes) % 16 == 0);
+  for (int d = 0; d < 8; ++d) {
+    kp.dst[d] = d < n_dst ? dst[d] : nullptr;
+    if (d < n_dst && (reinterpret_cast<uintptr_t>(dst[d]) & 15u)) vec_ok = false;
+  }
+  kp.Mb = a.Mb;
+  kp.nb_vec = a.Nb / VEC;
+  kp.ldc = a.ldc;
+  kp.out_dtype = a.out_dtype;
+  kp.vec_ok = vec_ok;
+  if (a.Nb % VEC) return B200S_ERR_BAD_SHAPE;
+  const int64_t blocks = (kp.Mb * kp.nb_vec + 255) / 256;
+  if (blocks > INT32_MAX) return B200S_ERR_BAD_SHAPE;
+  combine_peers_kernel<DEPTH, ALGO, TP><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
+
+template <int DEPTH, int ALGO>
+int launch_peers_dtype(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream) {
+  switch (a.prod_dtype) {
+    case B200S_BF16:
+      return launch_peers_one<DEPTH, ALGO, __nv_bfloat16>(a, dst, n_dst, stream);
+    case B200S_FP16:
+      return launch_peers_one<DEPTH, ALGO, __half>(a, dst, n_dst, stream);
+    case B200S_FP32:
+      return launch_peers_one<DEPTH, ALGO, float>(a, dst, n_dst, stream);
+  }
+  return B200S_ERR_BAD_DTYPE;
+}
+
 // ---- outer-quadrant form --------------------------------------------------------------------
 // One launch writes a few outer quadrants of C only, reading just the product groups that feed
 // them, so the pipelined driver can recombine a quadrant as soon as its last group is done.
@@ -407,6 +492,28 @@ int launch_combine_outer(const CombineOuterArgs& a, cudaStream_t stream) {
     return wino ? launch_outer_dtype<0, sched::kWinograd>(a, stream) : launch_outer_dtype<0, sched::kClassic>(a, stream);
   if (a.depth == 2)
     return wino ? launch_outer_dtype<1, sched::kWinograd>(a, stream) : launch_outer_dtype<1, sched::kClassic>(a, stream);
+  return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s
+
+namespace b200s {
+
+int launch_combine_peers(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream) {
+  const size_t pes = dtype_size(a.prod_dtype);
+  if (a.Mb <= 0 || a.Nb <= 0 || a.batch != 1 || n_dst < 1 || n_dst > 8 || !dst) return B200S_ERR_BAD_SHAPE;
+  if (a.Nb % static_cast<int>(16 / pes)) return B200S_ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(a.products) & 15u) return B200S_ERR_BAD_ALIGNMENT;
+  for (int d = 0; d < n_dst; ++d)
+    if (!dst[d]) return B200S_ERR_NULL_POINTER;
+  const bool wino = a.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && a.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (a.depth == 1)
+    return wino ? launch_peers_dtype<1, sched::kWinograd>(a, dst, n_dst, stream)
+                : launch_peers_dtype<1, sched::kClassic>(a, dst, n_dst, stream);
+  if (a.depth == 2)
+    return wino ? launch_peers_dtype<2, sched::kWinograd>(a, dst, n_dst, stream)
+                : launch_peers_dtype<2, sched::kClassic>(a, dst, n_dst, stream);
   return B200S_ERR_BAD_DEPTH;
 }
 

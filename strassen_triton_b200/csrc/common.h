@@ -74,6 +74,8 @@ struct CombineArgs {
   int algo, depth, prod_dtype, out_dtype, beta;
 };
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
+// The same recombination written to n_dst (<= 8) copies of C at once (a.C and a.beta are ignored).
+int launch_combine_peers(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream);
 
 
 // Outer-group forms used by the pipelined driver (api.cu): operand blocks of a few outer products,
