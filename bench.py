@@ -285,12 +285,12 @@ def run_gpu_arm(args):
         C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         p, _, _ = ops.make_problem(A, B, C[r0:r1], "classic", depth)
         ws = torch.empty(ops.workspace_bytes(p), dtype=torch.uint8, device=dev)
-        if args.exchange in ("peer", "peer_copy"):
+        if args.exchange.startswith("peer"):
             from strassen_triton_b200.sharded import PeerShardedMatmul
 
             del C, ws
             plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo="classic", depth=depth, panels=args.panels,
-                                     device=dev, exchange="copy" if args.exchange == "peer_copy" else "store")
+                                     device=dev, exchange={"peer": "store", "peer_push": "push", "peer_copy": "copy"}[args.exchange])
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
         else:
@@ -336,7 +336,7 @@ def run_gpu_arm(args):
         def e2e_step():
             dA = hA.to(dev, non_blocking=True)
             dB = hB.to(dev, non_blocking=True)
-            if args.exchange in ("peer", "peer_copy"):
+            if args.exchange.startswith("peer"):
                 out = plan(dA, dB)
             else:
                 out = sharded_matmul(dA, dB, n, panels=args.panels, out=C, algo="classic", depth=depth, workspace=ws)
@@ -415,7 +415,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--panels", type=int, default=2, help="row panels per rank for exchange/compute overlap (N > 1)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_copy", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_push", "peer_copy", "nccl"],
                     help="N > 1: 'peer' = recombination kernel stores into every rank's C over NVLink; "
                          "'nccl' = all-gather of the row blocks")
     args = ap.parse_args()

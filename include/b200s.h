@@ -211,6 +211,15 @@ int b200s_combine(const b200s_problem* p, const void* products_device, void* C_d
 int b200s_combine_peers(const b200s_problem* p, const void* products_device, void* const* C_list, int n_dst,
                         void* stream);
 
+/*
+ * Copies `bytes` (a multiple of 16, both ends 16-byte aligned) from src_device to n_dst (1..8)
+ * destinations, typically the same rows of C in the other GPUs' symmetric memory. The kernel keeps
+ * one small block per SM (no shared memory, few registers) so that it can run beside a resident
+ * GEMM CTA: the exchange of a finished row panel overlaps the products of the next one. No
+ * counterpart in the reference (it has no multi-GPU product).
+ */
+int b200s_push_rows(const void* src_device, void* const* dst_list, int n_dst, size_t bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

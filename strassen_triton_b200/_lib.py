@@ -82,6 +82,8 @@ SIGNATURES = {
     "b200s_preadd": (ctypes.c_int, [_P(Problem), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "b200s_combine_peers": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int,
                                            ctypes.c_void_p]),
+    "b200s_push_rows": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,
+                                       ctypes.c_void_p]),
     "b200s_combine": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
 }
 

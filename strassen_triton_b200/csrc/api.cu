@@ -428,6 +428,11 @@ int b200s_combine_peers(const b200s_problem* p, const void* products, void* cons
   return launch_combine_peers(c, C_list, n_dst, static_cast<cudaStream_t>(stream));
 }
 
+int b200s_push_rows(const void* src, void* const* dst_list, int n_dst, size_t bytes, void* stream) {
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  return launch_push_rows(src, dst_list, n_dst, bytes, static_cast<cudaStream_t>(stream));
+}
+
 int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* workspace,
                  size_t workspace_bytes, void* stream_v) {
   if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;

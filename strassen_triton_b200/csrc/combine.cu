@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
 #include <utility>
 
 #include "common.h"
@@ -515,6 +516,69 @@ int launch_combine_peers(const CombineArgs& a, void* const* dst, int n_dst, cuda
     return wino ? launch_peers_dtype<2, sched::kWinograd>(a, dst, n_dst, stream)
                 : launch_peers_dtype<2, sched::kClassic>(a, dst, n_dst, stream);
   return B200S_ERR_BAD_DEPTH;
+}
+
+}  // namespace b200s
+
+namespace b200s {
+
+namespace {
+// Copies a contiguous byte range to several destinations (other GPUs' memory mapped into this
+// process). One 256-thread block per SM with a handful of registers and no shared memory, so it
+// runs beside a resident GEMM CTA: the rows of a finished panel cross NVLink while the tensor
+// cores work on the next panel.
+struct PushParams {
+  const uint4* src;
+  uint4* dst[8];
+  int32_t n_dst;
+  int64_t n_vec;
+};
+
+__global__ void __launch_bounds__(256) push_rows_kernel(const PushParams p) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < p.n_vec; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(p.src + i + u * stride);
+#pragma unroll 1
+    for (int d = 0; d < p.n_dst; ++d)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) p.dst[d][i + u * stride] = v[u];
+  }
+  for (; i < p.n_vec; i += stride) {
+    const uint4 v = __ldcs(p.src + i);
+    for (int d = 0; d < p.n_dst; ++d) p.dst[d][i] = v;
+  }
+}
+}  // namespace
+
+int launch_push_rows(const void* src, void* const* dst, int n_dst, size_t bytes, cudaStream_t stream) {
+  if (!src || !dst) return B200S_ERR_NULL_POINTER;
+  if (n_dst < 1 || n_dst > 8 || bytes == 0 || bytes % 16) return B200S_ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(src) & 15u) return B200S_ERR_BAD_ALIGNMENT;
+  PushParams kp;
+  kp.src = static_cast<const uint4*>(src);
+  kp.n_dst = n_dst;
+  kp.n_vec = static_cast<int64_t>(bytes / 16);
+  for (int d = 0; d < 8; ++d) {
+    kp.dst[d] = d < n_dst ? static_cast<uint4*>(dst[d]) : nullptr;
+    if (d < n_dst && (!dst[d] || (reinterpret_cast<uintptr_t>(dst[d]) & 15u))) return B200S_ERR_BAD_ALIGNMENT;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return B200S_ERR_NO_DEVICE;
+  int64_t blocks = (kp.n_vec + 255) / 256;
+  if (blocks > sms) blocks = sms;
+  // Ask for the same shared-memory carve-out the GEMM CTAs run with, so that an SM does not have
+  // to drain before it can host a block of this kernel beside one of them.
+  static std::once_flag carve;
+  std::call_once(carve, [] {
+    cudaFuncSetAttribute(push_rows_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  });
+  push_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(kp);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
 }
 
 }  // namespace b200s

@@ -76,6 +76,8 @@ struct CombineArgs {
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 // The same recombination written to n_dst (<= 8) copies of C at once (a.C and a.beta are ignored).
 int launch_combine_peers(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream);
+// Contiguous copy of `bytes` (a multiple of 16) from src to n_dst (<= 8) destinations, small SM footprint.
+int launch_push_rows(const void* src, void* const* dst, int n_dst, size_t bytes, cudaStream_t stream);
 
 
 // Outer-group forms used by the pipelined driver (api.cu): operand blocks of a few outer products,

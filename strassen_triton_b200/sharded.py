@@ -153,8 +153,8 @@ class PeerShardedMatmul:
         if depth not in (1, 2):
             raise ValueError("depth must be 1 or 2 (a dense product has no recombination to fuse into)")
         self.M, self.N, self.K, self.dtype, self.algo, self.depth = M, N, K, dtype, algo, depth
-        if exchange not in ("store", "copy"):
-            raise ValueError("exchange must be 'store' or 'copy'")
+        if exchange not in ("store", "copy", "push"):
+            raise ValueError("exchange must be 'store', 'push' or 'copy'")
         self.exchange = exchange
         self.rows = M // self.world
         quantum = 8 << depth
@@ -177,6 +177,7 @@ class PeerShardedMatmul:
         # products on a high-priority stream, the NVLink-bound recombination on a low-priority one
         self.hi = torch.cuda.Stream(self.device, priority=-1)
         self.side = torch.cuda.Stream(self.device, priority=0)
+        self.copy_streams = [torch.cuda.Stream(self.device) for _ in range(self.world)]
         self.ev_gemm = [torch.cuda.Event() for _ in range(panels)]
         self.ev_comb = [torch.cuda.Event() for _ in range(panels)]
         self._es = es
@@ -222,6 +223,17 @@ class PeerShardedMatmul:
                     self._lib.check(lib.b200s_combine_peers(ctypes.byref(prob), mp.data_ptr(), dst, self.world,
                                                             self.side.cuda_stream))
                     self.ev_comb[i].record(self.side)
+                elif self.exchange == "push":
+                    # recombine into the local C at full occupancy, then a small-footprint kernel that
+                    # fits beside the next panel's GEMM CTAs stores the rows into the peers' C
+                    self._lib.check(lib.b200s_combine(ctypes.byref(prob), mp.data_ptr(), c_rows.data_ptr(),
+                                                      self.side.cuda_stream))
+                    self.ev_comb[i].record(self.side)
+                    if self.world > 1:
+                        peers = [ptr + row0 * self.N * self._es for r, ptr in enumerate(self.peer_ptrs) if r != self.rank]
+                        dst = (ctypes.c_void_p * len(peers))(*peers)
+                        self._lib.check(lib.b200s_push_rows(c_rows.data_ptr(), dst, len(peers),
+                                                            self.prow * self.N * self._es, self.side.cuda_stream))
                 else:
                     # recombine into the local C, then let the copy engines push the finished rows to
                     # the peers: no SM is held while the bytes cross NVLink
@@ -230,10 +242,17 @@ class PeerShardedMatmul:
                     self.ev_comb[i].record(self.side)
                     for r in range(self.world):
                         if r != self.rank:
-                            peer_rows = self.hdl.get_buffer(r, (self.prow, self.N), self.dtype, row0 * self.N)
-                            peer_rows.copy_(c_rows, non_blocking=True)
+                            # one stream per peer, so the transfers to different peers run side by side
+                            cs = self.copy_streams[r]
+                            cs.wait_event(self.ev_comb[i])
+                            with torch.cuda.stream(cs):
+                                peer_rows = self.hdl.get_buffer(r, (self.prow, self.N), self.dtype, row0 * self.N)
+                                peer_rows.copy_(c_rows, non_blocking=True)
         user.wait_stream(main)
         user.wait_stream(self.side)
+        if self.exchange == "copy":
+            for cs in self.copy_streams:
+                user.wait_stream(cs)
         for t in (A_block, B):
             t.record_stream(main)
         self.hdl.barrier(channel=1)          # every rank's stores have been issued and completed

@@ -32,7 +32,7 @@ def single_rank_group(built_library):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["store", "copy"])
+@pytest.mark.parametrize("exchange", ["store", "push", "copy"])
 @pytest.mark.parametrize("panels", [1, 2])
 def test_peer_sharded_plan_single_rank(single_rank_group, exchange, panels):
     from strassen_triton_b200 import ops
