@@ -414,7 +414,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--panels", type=int, default=2, help="row panels per rank for exchange/compute overlap (N > 1)")
+    ap.add_argument("--panels", type=int, default=1, help="row panels per rank for exchange/compute overlap (N > 1)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "peer_push", "peer_copy", "nccl"],
                     help="N > 1: 'peer' = recombination kernel stores into every rank's C over NVLink; "
                          "'nccl' = all-gather of the row blocks")
