@@ -338,51 +338,77 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int col0 = nt * BN_TILE + half * BNH;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                              static_cast<uint32_t>(buf * BN_TILE + half * BNH);
-      if (p.tma_store) {
-        // 128-byte row groups: tcgen05.ld -> convert -> swizzled st.shared -> one TMA store of a
-        // 32-row x 128-byte box per group.
-        const int cols_per_group = out_es == 4 ? 32 : 64;
-#pragma unroll 1
-        for (int gc = 0; gc < BNH; gc += cols_per_group) {
-          const uint32_t sbuf = stg + static_cast<uint32_t>(stage_flip) * 4096u;
-          const uint32_t srow = sbuf + static_cast<uint32_t>(lane) * 128u;
+      bool released = false;
+      auto release_accumulator = [&]() {
+        // every tcgen05.ld of this warp has completed: hand the accumulator back to the MMA warp
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtaGroup == 2)
+            ptx::mbar_arrive_cluster(tempty_bar(buf), 0);
+          else
+            ptx::mbar_arrive(tempty_bar(buf));
+        }
+        released = true;
+      };
+      auto stage_and_store = [&](const uint32_t (&h)[32], int gc) {
+        const uint32_t sbuf = stg + static_cast<uint32_t>(stage_flip) * 4096u;
+        const uint32_t srow = sbuf + static_cast<uint32_t>(lane) * 128u;
+        // the store that last read this staging buffer must be done with it
+        if (lane == 0) ptx::tma_store_wait_read<STG_BUFS - 1>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          ptx::st_shared_v4(srow + ((static_cast<uint32_t>(j) ^ sw) << 4), h[4 * j], h[4 * j + 1], h[4 * j + 2],
+                            h[4 * j + 3]);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_3d(&tmC, sbuf, col0 + gc, row_warp, b);
+          ptx::tma_store_commit();
+        }
+        if constexpr (STG_BUFS == 2) stage_flip ^= 1;
+      };
+      if (p.tma_store && out_es == 2) {
+        // 128-byte row groups of 64 columns: tcgen05.ld -> convert -> swizzled st.shared -> one TMA
+        // store of a 32-row x 128-byte box. The loads of group g+1 are in flight while group g is
+        // staged and stored.
+        constexpr int kGroups = BNH / 64;
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32(taddr, r0);
+        ptx::tmem_ld_32x32(taddr + 32, r1);
+#pragma unroll
+        for (int g = 0; g < kGroups; ++g) {
+          ptx::tmem_ld_wait();
           uint32_t h[32];
-          if (out_es == 4) {
-            ptx::tmem_ld_32x32(taddr + gc, h);
-            ptx::tmem_ld_wait();
+          if (out_dt == B200S_BF16) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              h[j] = ptx::pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              h[16 + j] = ptx::pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+            }
           } else {
-            uint32_t r0[32], r1[32];
-            ptx::tmem_ld_32x32(taddr + gc, r0);
-            ptx::tmem_ld_32x32(taddr + gc + 32, r1);
-            ptx::tmem_ld_wait();
-            if (out_dt == B200S_BF16) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                h[j] = ptx::pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-                h[16 + j] = ptx::pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                h[j] = ptx::pack_f16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-                h[16 + j] = ptx::pack_f16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-              }
+            for (int j = 0; j < 16; ++j) {
+              h[j] = ptx::pack_f16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+              h[16 + j] = ptx::pack_f16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
             }
           }
-          // the store that last read this staging buffer must be done with it
-          if (lane == 0) ptx::tma_store_wait_read<STG_BUFS - 1>();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            ptx::st_shared_v4(srow + ((static_cast<uint32_t>(j) ^ sw) << 4), h[4 * j], h[4 * j + 1], h[4 * j + 2],
-                              h[4 * j + 3]);
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_3d(&tmC, sbuf, col0 + gc, row_warp, b);
-            ptx::tma_store_commit();
+          if (g + 1 < kGroups) {
+            ptx::tmem_ld_32x32(taddr + (g + 1) * 64, r0);
+            ptx::tmem_ld_32x32(taddr + (g + 1) * 64 + 32, r1);
+          } else {
+            release_accumulator();
           }
-          if constexpr (STG_BUFS == 2) stage_flip ^= 1;
+          stage_and_store(h, g * 64);
+        }
+      } else if (p.tma_store) {
+#pragma unroll 1
+        for (int gc = 0; gc < BNH; gc += 32) {
+          uint32_t h[32];
+          ptx::tmem_ld_32x32(taddr + gc, h);
+          ptx::tmem_ld_wait();
+          stage_and_store(h, gc);
         }
       } else {
         uint8_t* crow = static_cast<uint8_t*>(p.C) +
@@ -404,15 +430,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
-      // All tcgen05.ld of this warp have completed: hand the accumulator back.
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (kCtaGroup == 2)
-          ptx::mbar_arrive_cluster(tempty_bar(buf), 0);
-        else
-          ptx::mbar_arrive(tempty_bar(buf));
-      }
+      if (!released) release_accumulator();
     }
     if (p.tma_store && lane == 0) ptx::tma_store_wait_all<0>();  // shared memory must outlive the stores
     __syncwarp();
