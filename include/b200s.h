@@ -56,7 +56,8 @@ typedef enum b200s_algo {
 /* How fp32 inputs reach the tensor cores. */
 typedef enum b200s_precision {
   B200S_PREC_TF32 = 0,  /* one TF32 pass (10-bit mantissa operands), what torch does with allow_tf32 */
-  B200S_PREC_3XTF32 = 1 /* split each operand into hi+lo TF32 parts, three passes, ~fp32 accuracy */
+  B200S_PREC_3XTF32 = 1 /* split each operand into hi+lo TF32 parts, three passes: operands keep their fp32
+                           mantissa, error ~1e-5 at K = 1024 (left by the tensor core's fp32 accumulation) */
 } b200s_precision;
 
 /*
@@ -146,7 +147,7 @@ int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_dev
  * Limit: b200s_workspace_bytes(p) must not exceed 64 MiB (for bf16: depth 1 up to about 2048^3,
  * depth 2 up to about 1792^3; any size at depth 0); larger problems return B200S_ERR_TOO_LARGE and
  * launch nothing. Always the sequential schedule on `stream`; `pipeline` and `b_blocks_ready` are
- * ignored.
+ * ignored, and fp32 operands always run as one TF32 pass.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and the
  * device's properties; make that first call outside any stream capture. All calls share the one

@@ -104,6 +104,8 @@ struct Plan {
   int64_t Mb, Nb, Kb;       // block extents
   size_t sa_bytes, sb_bytes, mp_bytes;
   size_t ta_bytes, tb_bytes;  // K-major copies of fp32 operands given MN-major
+  size_t a3_bytes, b3_bytes;  // hi/lo split operands of the three-pass TF32 mode
+  bool split3;
   size_t total_bytes;
 };
 
@@ -119,6 +121,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   if (p->depth < -1 || p->depth > 2) return B200S_ERR_BAD_DEPTH;
   if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
   if (p->pipeline < 0 || p->pipeline > 2) return B200S_ERR_BAD_SHAPE;
+  if (p->precision != B200S_PREC_TF32 && p->precision != B200S_PREC_3XTF32) return B200S_ERR_BAD_DTYPE;
   if (p->b_blocks_ready != 0 && p->b_blocks_ready != 1) return B200S_ERR_BAD_SHAPE;
   const int64_t a_cols = p->a_major == B200S_K_MAJOR ? p->K : p->M;
   const int64_t b_cols = p->b_major == B200S_K_MAJOR ? p->K : p->N;
@@ -165,9 +168,17 @@ int make_plan(const b200s_problem* p, Plan* plan) {
     if (p->a_major == B200S_MN_MAJOR) plan->ta_bytes = round256(b * p->M * p->K * 4);
     if (p->b_major == B200S_MN_MAJOR) plan->tb_bytes = round256(b * p->K * p->N * 4);
   }
+  plan->a3_bytes = plan->b3_bytes = 0;
+  plan->split3 = p->in_dtype == B200S_FP32 && p->precision == B200S_PREC_3XTF32;
+  if (plan->split3) {
+    if (p->K % 4) return B200S_ERR_BAD_SHAPE;
+    const size_t nb3 = static_cast<size_t>(p->batch) * static_cast<size_t>(plan->np);
+    plan->a3_bytes = round256(nb3 * plan->Mb * plan->Kb * 3 * 4);
+    plan->b3_bytes = round256(nb3 * plan->Nb * plan->Kb * 3 * 4);
+  }
   if (depth == 0) {
     plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = 0;
-    plan->total_bytes = plan->ta_bytes + plan->tb_bytes;
+    plan->total_bytes = plan->ta_bytes + plan->tb_bytes + plan->a3_bytes + plan->b3_bytes;
     return B200S_OK;
   }
   const size_t es = dtype_size(p->in_dtype), ps = dtype_size(pd);
@@ -175,7 +186,8 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   plan->sa_bytes = round256(nb * plan->Mb * plan->Kb * es);
   plan->sb_bytes = round256(nb * plan->Kb * plan->Nb * es);
   plan->mp_bytes = round256(nb * plan->Mb * plan->Nb * ps);
-  plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes + plan->ta_bytes + plan->tb_bytes;
+  plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes + plan->ta_bytes + plan->tb_bytes +
+                      plan->a3_bytes + plan->b3_bytes;
   return B200S_OK;
 }
 
@@ -476,6 +488,8 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   g.in_dtype = p->in_dtype;
   g.a_major = p->a_major;
   g.b_major = p->b_major;
+  uint8_t* A3 = ws + plan.sa_bytes + plan.sb_bytes + plan.mp_bytes + plan.ta_bytes + plan.tb_bytes;
+  uint8_t* B3 = A3 + plan.a3_bytes;
   if (plan.depth == 0) {
     g.A = A, g.B = B, g.C = C;
     g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
@@ -483,6 +497,16 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
     g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
     g.out_dtype = p->out_dtype;
     g.beta = p->beta;
+    if (plan.split3) {
+      // both operands are K-major here; the product runs over the three K segments
+      rc = launch_split3_f32(A, A3, p->M, p->K, p->lda, p->batch, p->strideA, 0, stream);
+      if (rc) return rc;
+      rc = launch_split3_f32(B, B3, p->N, p->K, p->ldb, p->batch, p->strideB, 1, stream);
+      if (rc) return rc;
+      g.A = A3, g.B = B3, g.K = 3 * p->K;
+      g.lda = g.ldb = 3 * p->K;
+      g.strideA = p->M * 3 * p->K, g.strideB = p->N * 3 * p->K;
+    }
     return launch_gemm(g, stream);
   }
 
@@ -493,7 +517,7 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   // Large single products run the pipelined driver unless the caller chose otherwise.
   const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
   const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 24576.0 * 24576.0 * 24576.0);
-  if (p->batch == 1 && pipelined) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
+  if (p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 
   rc = b200s_preadd(p, 0, A, Sa, stream_v);
   if (rc) return rc;
@@ -514,6 +538,19 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   g.strideC = plan.Mb * plan.Nb;
   g.out_dtype = plan.prod_dtype;
   g.beta = 0;
+  if (plan.split3) {
+    // operand blocks are K-major fp32: split every block row into its three K segments
+    const int64_t nblk = p->batch * plan.np;
+    rc = launch_split3_f32(Sa, A3, nblk * plan.Mb, plan.Kb, plan.Kb, 1, 0, 0, stream);
+    if (rc) return rc;
+    if (!p->b_blocks_ready) {
+      rc = launch_split3_f32(Sb, B3, nblk * plan.Nb, plan.Kb, plan.Kb, 1, 0, 1, stream);
+      if (rc) return rc;
+    }
+    g.A = A3, g.B = B3, g.K = 3 * plan.Kb;
+    g.lda = g.ldb = 3 * plan.Kb;
+    g.strideA = plan.Mb * 3 * plan.Kb, g.strideB = plan.Nb * 3 * plan.Kb;
+  }
   rc = launch_gemm(g, stream);
   if (rc) return rc;
 
@@ -569,6 +606,9 @@ int static_state(StaticState** out) {
 
 int b200s_matmul_static(const b200s_problem* p_in, const void* A, const void* B, void* C, void* stream_v) {
   if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;
+  b200s_problem single_pass = *p_in;
+  single_pass.precision = B200S_PREC_TF32;  // this entry runs fp32 operands as one TF32 pass
+  p_in = &single_pass;
   Plan plan;
   int rc = make_plan(p_in, &plan);
   if (rc) return rc;

@@ -53,6 +53,10 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 int launch_transpose_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
                          int64_t batch, int64_t stride_in, int64_t stride_out, cudaStream_t stream);
 
+// Three-pass TF32: out = rows x 3*cols with K segments [hi|lo|hi] (side 0) or [hi|hi|lo] (side 1).
+int launch_split3_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t batch,
+                      int64_t stride_in, int side, cudaStream_t stream);
+
 // ---- Strassen schedule (schedule.h) and its passes (preadd.cu, combine.cu) ----------------
 struct PreaddArgs {
   const void* X;   // one operand, storage rows x cols with the contiguous dimension last

@@ -4,6 +4,8 @@
 // plain 128-byte swizzle this library's TMA maps use, so an fp32 operand whose outer dimension is
 // contiguous (for example B of a row-major A @ B) is first rewritten K-major into scratch.
 // 16-bit operands never take this path: the tensor core reads both of their majors directly.
+//
+// Also here: the hi/lo split of fp32 operands for the three-pass TF32 mode (B200S_PREC_3XTF32).
 
 #include <cuda_runtime.h>
 
@@ -34,7 +36,46 @@ __global__ void __launch_bounds__(256) transpose32_kernel(const float* __restric
   }
 }
 
+// hi = x rounded to TF32 (10-bit mantissa), lo = x - hi rounded to TF32. x.y ~ hi.hi' + lo.hi' + hi.lo'
+// with the dropped lo.lo' term about 2^-22 of the product.
+__device__ __forceinline__ float tf32_round(float x) {
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
+
+// in: rows x cols fp32 (ld_in); out: rows x 3*cols, three K segments per row:
+// side 0 (A): [hi | lo | hi], side 1 (B): [hi | hi | lo].
+__global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows,
+                                                     int64_t cols4, int64_t ld_in, int64_t stride_in, int side) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * cols4) return;
+  const int64_t r = idx / cols4, c4 = idx - r * cols4;
+  const int64_t cols = cols4 * 4;
+  const float4 x = *reinterpret_cast<const float4*>(in + static_cast<int64_t>(blockIdx.y) * stride_in + r * ld_in + c4 * 4);
+  float4 hi, lo;
+  hi.x = tf32_round(x.x), hi.y = tf32_round(x.y), hi.z = tf32_round(x.z), hi.w = tf32_round(x.w);
+  lo.x = tf32_round(x.x - hi.x), lo.y = tf32_round(x.y - hi.y), lo.z = tf32_round(x.z - hi.z), lo.w = tf32_round(x.w - hi.w);
+  float* o = out + (static_cast<int64_t>(blockIdx.y) * rows + r) * (3 * cols) + c4 * 4;
+  *reinterpret_cast<float4*>(o) = hi;
+  *reinterpret_cast<float4*>(o + cols) = side == 0 ? lo : hi;
+  *reinterpret_cast<float4*>(o + 2 * cols) = side == 0 ? hi : lo;
+}
+
 }  // namespace
+
+int launch_split3_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t batch,
+                      int64_t stride_in, int side, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || batch <= 0 || batch > 65535 || cols % 4) return B200S_ERR_BAD_SHAPE;
+  if ((ld_in * 4) % 16 || (reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+    return B200S_ERR_BAD_ALIGNMENT;
+  const int64_t blocks = (rows * (cols / 4) + 255) / 256;
+  if (blocks > INT32_MAX) return B200S_ERR_BAD_SHAPE;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(batch));
+  split3_kernel<<<grid, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), rows, cols / 4, ld_in,
+                                          stride_in, side);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
 
 int launch_transpose_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
                          int64_t batch, int64_t stride_in, int64_t stride_out, cudaStream_t stream) {

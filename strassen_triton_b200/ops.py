@@ -18,6 +18,18 @@ _ALGO = {"auto": _lib.ALGO_AUTO, "dense": _lib.ALGO_DENSE, "classic": _lib.ALGO_
          "strassen": _lib.ALGO_CLASSIC, "winograd": _lib.ALGO_WINOGRAD}
 
 
+def resolve_precision(precision):
+    """How fp32 operands reach the tensor cores: "tf32" (one pass) or "3xtf32" (hi/lo split, three
+    passes, fp32-level accuracy). ``None`` follows ``torch.backends.cuda.matmul.allow_tf32``, the
+    switch the reference's scripts set (main_profiling.py:31-34): TF32 when it is on, else the
+    three-pass mode, as torch.mm would then compute in full fp32."""
+    if precision is None:
+        return "tf32" if torch.backends.cuda.matmul.allow_tf32 else "3xtf32"
+    if precision not in ("tf32", "3xtf32"):
+        raise ValueError("precision must be 'tf32', '3xtf32' or None")
+    return precision
+
+
 def _require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if not isinstance(t, torch.Tensor):
@@ -54,7 +66,7 @@ def _operand(t: torch.Tensor):
     return (t,) + got
 
 
-def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precision="tf32",
+def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precision=None,
                  tile_variant=0, pipeline=0, b_blocks_ready=False):
     """Fill a ``b200s_problem`` for C (+)= A @ B. Returns (problem, A', B') where A'/B' are the
     tensors whose pointers must be passed (copies only when the strides force one)."""
@@ -88,7 +100,7 @@ def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precis
     p.depth = int(depth)
     p.beta = int(beta)
     p.prod_dtype = -1 if prod_dtype is None else _DTYPE[prod_dtype]
-    p.precision = _lib.PREC_3XTF32 if precision == "3xtf32" else _lib.PREC_TF32
+    p.precision = _lib.PREC_3XTF32 if resolve_precision(precision) == "3xtf32" else _lib.PREC_TF32
     p.tile_variant = int(tile_variant)
     p.pipeline = int(pipeline)
     p.b_blocks_ready = 1 if b_blocks_ready else 0
@@ -108,7 +120,7 @@ def resolve(p: "_lib.Problem"):
 
 
 def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto", depth=-1, beta=0,
-               prod_dtype=None, precision="tf32", tile_variant=0, pipeline=0, b_blocks_ready=False,
+               prod_dtype=None, precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False,
                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B (beta=0) or C += A @ B (beta=1) on the current CUDA stream. Returns C."""
     _require_cuda(A, B, C)
@@ -131,7 +143,7 @@ def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto"
 
 
 def matmul(A: torch.Tensor, B: torch.Tensor, *, algo="auto", depth=-1, out_dtype=None, prod_dtype=None,
-           precision="tf32", tile_variant=0, pipeline=0, b_blocks_ready=False, workspace=None) -> torch.Tensor:
+           precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, workspace=None) -> torch.Tensor:
     """A @ B as a new tensor of ``out_dtype`` (default: the operand dtype)."""
     _require_cuda(A, B)
     shape = (A.shape[-2], B.shape[-1]) if A.dim() == 2 else (A.shape[0], A.shape[-2], B.shape[-1])
