@@ -105,6 +105,11 @@ def load() -> ctypes.CDLL:
                 fn = getattr(lib, name)
                 fn.restype = res
                 fn.argtypes = args
+            # measured (M, N, K) -> (algo, depth) table shipped beside the library; a missing or
+            # corrupt file leaves the library's built-in thresholds in force
+            table = os.path.join(PKG_DIR, "tuner_table.txt")
+            if os.path.exists(table):
+                lib.b200s_tuner_load(table.encode())
             _lib = lib
     return _lib
 

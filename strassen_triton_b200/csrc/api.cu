@@ -68,17 +68,16 @@ double log_volume(int64_t M, int64_t N, int64_t K) {
   return std::log2(static_cast<double>(M)) + std::log2(static_cast<double>(N)) + std::log2(static_cast<double>(K));
 }
 
-// Built-in choice when the table holds nothing for the dtype: dense below a cube of
-// kDefaultCrossover, one Strassen level above it, two above twice that.
-constexpr int64_t kDefaultCrossover = 8192;
+// Built-in choice when the table holds nothing for the dtype: a dense product below a cube of
+// kDefaultCrossover, two Strassen levels from there on (measured on B200, bf16: at 8192^3 the dense
+// kernel wins, at 16384^3 and 32768^3 two levels win over one level and over dense).
+constexpr int64_t kDefaultCrossover = 12288;
 
 void default_choice(int64_t M, int64_t N, int64_t K, int32_t* algo, int32_t* depth) {
   const double v = log_volume(M, N, K);
   const double c1 = 3.0 * std::log2(static_cast<double>(kDefaultCrossover));
   if (v < c1) {
     *algo = B200S_ALGO_DENSE, *depth = 0;
-  } else if (v < c1 + 3.0) {
-    *algo = B200S_ALGO_CLASSIC, *depth = 1;
   } else {
     *algo = B200S_ALGO_CLASSIC, *depth = 2;
   }
