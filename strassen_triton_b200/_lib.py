@@ -10,7 +10,8 @@ import os
 import threading
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libb200s.so")
+# B200S_LIBRARY names another build of the same library (A/B comparisons of kernel variants).
+LIB_PATH = os.environ.get("B200S_LIBRARY") or os.path.join(PKG_DIR, "libb200s.so")
 
 # enums of include/b200s.h
 BF16, FP16, FP32 = 0, 1, 2
