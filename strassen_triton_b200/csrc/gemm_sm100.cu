@@ -373,33 +373,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // 128-byte row groups of 64 columns: tcgen05.ld -> convert -> swizzled st.shared -> one TMA
         // store of a 32-row x 128-byte box. The loads of group g+1 are in flight while group g is
         // staged and stored.
-        constexpr int kGroups = BNH / 64;
-        uint32_t r0[32], r1[32];
-        ptx::tmem_ld_32x32(taddr, r0);
-        ptx::tmem_ld_32x32(taddr + 32, r1);
+        // First the whole accumulator goes to registers (converted, 128 packed words per thread) and
+        // is handed back, then the staging and the stores run while the MMA warp already works on
+        // the next tile.
+        constexpr int kChunks = BNH / 32;
+        uint32_t hp[kChunks * 16];
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr, r);
 #pragma unroll
-        for (int g = 0; g < kGroups; ++g) {
+        for (int c = 0; c < kChunks; ++c) {
           ptx::tmem_ld_wait();
-          uint32_t h[32];
           if (out_dt == B200S_BF16) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              h[j] = ptx::pack_bf16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-              h[16 + j] = ptx::pack_bf16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-            }
+            for (int j = 0; j < 16; ++j)
+              hp[c * 16 + j] = ptx::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              h[j] = ptx::pack_f16(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-              h[16 + j] = ptx::pack_f16(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-            }
+            for (int j = 0; j < 16; ++j)
+              hp[c * 16 + j] = ptx::pack_f16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           }
-          if (g + 1 < kGroups) {
-            ptx::tmem_ld_32x32(taddr + (g + 1) * 64, r0);
-            ptx::tmem_ld_32x32(taddr + (g + 1) * 64 + 32, r1);
-          } else {
-            release_accumulator();
-          }
+          if (c + 1 < kChunks) ptx::tmem_ld_32x32(taddr + (c + 1) * 32, r);
+        }
+        release_accumulator();
+#pragma unroll
+        for (int g = 0; g < kChunks / 2; ++g) {
+          uint32_t h[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) h[j] = hp[g * 32 + j];
           stage_and_store(h, g * 64);
         }
       } else if (p.tma_store) {
