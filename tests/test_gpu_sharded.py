@@ -67,3 +67,24 @@ def test_nccl_sharded_matmul_single_rank(single_rank_group):
     C = sharded_matmul(A, B, M, group=single_rank_group, panels=2, algo="classic", depth=1)
     ref = A.double() @ B.double()
     assert ((C.double() - ref).norm() / ref.norm()).item() < 1e-2
+
+
+def test_fsdp_gpt2_steps_single_rank(single_rank_group):
+    """Two GPT-2 blocks under FSDP (bf16 mixed precision, use_orig_params) with every Linear a
+    LinearStrassen: a few optimizer steps on random tokens run through the library's kernels in
+    forward and backward, the loss starts at ln(vocab) and stays finite."""
+    import math
+
+    from strassen_triton_b200 import _lib, ops
+    from strassen_triton_b200.fsdp_gpt2 import VOCAB_PADDED, build, train_steps
+
+    torch.manual_seed(0)
+    model = build(layers=2, seq=128, depth=None, device="cuda", world=1)
+    n0 = _lib.load().b200s_launch_count()
+    losses = train_steps(model, 4, batch=4, seq=128, rank=0)
+    assert all(math.isfinite(x) for x in losses)
+    assert abs(losses[0] - math.log(VOCAB_PADDED)) < 0.5
+    assert losses[-1] < losses[0] + 0.5
+    # 9 Linears (4 per block + lm_head), forward + two backward products each, 4 steps
+    assert _lib.load().b200s_launch_count() - n0 >= 9 * 3 * 4
+    assert ops.device_status() == (0, 0)
