@@ -73,7 +73,7 @@ class GPT(nn.Module):
         for blk in self.blocks:
             x = blk(x)
         logits = self.lm_head(self.ln_f(x))
-        return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.view(-1))
+        return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
 
 
 def build(layers, seq, depth, device, world):
