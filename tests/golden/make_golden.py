@@ -61,7 +61,9 @@ CASES = [
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of vmad18/strassen-triton>")
+    ref_dir = sys.argv[1]
     sys.path.insert(0, ref_dir)
     import importlib
 
