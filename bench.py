@@ -188,11 +188,11 @@ def run_reference_arm(args):
 def workload_config(n_gpus):
     if n_gpus == 1:
         return {"workload": "two-level Strassen C=A.B, M=N=K=16384, bf16 inputs U(-1,1) seed 0, fp32 accumulation "
-                            "and aggregation, bf16 output (BASELINE configs[2])",
+                            "and aggregation, bf16 output (the headline configuration)",
                 "M": 16384, "N": 16384, "K": 16384, "depth": 2, "algo": "classic",
                 "l2": "inputs (1.6 GB) exceed L2 (126 MB); no flush between steps"}
     return {"workload": f"row-sharded two-level Strassen, M=N=K=32768, bf16 inputs N(0,1)/sqrt(K), A in {n_gpus} row "
-                        "blocks, B replicated, NCCL all-gather of C (BASELINE configs[4])",
+                        "blocks, B replicated, every rank ends with the whole C (the multi-GPU configuration)",
             "M": 32768, "N": 32768, "K": 32768, "depth": 2, "algo": "classic", "parallelism": f"rowshard{n_gpus}",
             "l2": "inputs exceed L2 (126 MB); no flush between steps"}
 

@@ -11,7 +11,7 @@ reduce-scatter.
     torchrun --nproc-per-node 8 -m strassen_triton_b200.fsdp_gpt2 --steps 10
     python -m strassen_triton_b200.fsdp_gpt2 --layers 2 --steps 3          # one GPU
 
-BASELINE config 5b: 12 layers, d = 768, 12 heads, vocab 50257 (padded to 50304 rows so that every
+The reference's training configuration at GPT-2-124M size: 12 layers, d = 768, 12 heads, vocab 50257 (padded to 50304 rows so that every
 matrix row is a whole number of 16-byte vectors), sequence 1024, 8 sequences per GPU.
 """
 from __future__ import annotations

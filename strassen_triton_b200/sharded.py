@@ -4,7 +4,7 @@ A is split into contiguous row blocks, one per rank; B is replicated; every rank
 Strassen pipeline of libb200s.so on its (M/P) x K block and the bf16 row blocks of C are exchanged
 with one all-gather (NCCL over NVLink on GPUs). Row panels let the gather of panel i overlap the
 product of panel i+1. The reference has no multi-GPU product; this is the partition its
-north-star configuration names (M = N = K = 32768 over 1/2/4/8 GPUs).
+multi-GPU configuration names (M = N = K = 32768 over 1/2/4/8 GPUs).
 """
 from __future__ import annotations
 

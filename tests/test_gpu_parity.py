@@ -92,7 +92,7 @@ def test_dense_tf32_all_majors(ops, a_t, b_t):
 @pytest.mark.parametrize("a_t,b_t", [(False, False), (True, True)])
 @pytest.mark.parametrize("algo,depth", [("dense", 0), ("classic", 1), ("classic", 2), ("winograd", 1)])
 def test_fp32_three_pass_tf32_reaches_fp32_accuracy(ops, a_t, b_t, algo, depth):
-    """BASELINE config 1 (1024^3 fp32 N(0,1)): with the hi/lo split the operands carry their full
+    """The fp32 configuration (1024^3, N(0,1)): with the hi/lo split the operands carry their full
     fp32 mantissa and the error against fp64 drops from TF32's 6e-4 to about 1e-5. What remains is
     the tensor core's own fp32 accumulation (it does not round to nearest), so the reference's CPU
     fp32 run (5.8e-7 one level, 1.2e-6 two levels) stays about 20x tighter; the bound here is 3e-5."""
@@ -152,7 +152,7 @@ def test_strassen_rectangular_and_transposed(ops, shape, a_t, b_t):
 
 @pytest.mark.parametrize("depth", [1, 2])
 def test_error_is_no_worse_than_the_reference(ops, depth):
-    """Against fp64, at the same depth and dtype, on U(-1,1) bf16 inputs (BASELINE config 3's
+    """Against fp64, at the same depth and dtype, on U(-1,1) bf16 inputs (the 16384^3 configuration's
     distribution at a size the CPU oracle finishes in seconds)."""
     n = 1024
     A, B = seeded_pair(0, (n, n), (n, n), dist="uniform")
@@ -298,7 +298,7 @@ def test_functional_entry_points(ops):
 @pytest.mark.parametrize("shape", [(8192, 768, 3072), (8192, 3072, 768), (8192, 768, 2304), (2048, 2048, 2048)])
 @pytest.mark.parametrize("depth", [0, 1])
 def test_linear_forward_backward(ops, shape, depth):
-    """BASELINE config 4: X ~ N(0,1), W ~ N(0, 0.02), dY ~ N(0,1); Y, dX, dW against fp64 autograd."""
+    """GPT-2-124M Linear shapes: X ~ N(0,1), W ~ N(0, 0.02), dY ~ N(0,1); Y, dX, dW against fp64 autograd."""
     from model.layers import LinearStrassen
 
     M, din, dout = shape
@@ -340,9 +340,9 @@ def test_linear_under_autocast(ops):
 # ------------------------------------------------------------------ full-size properties
 
 @pytest.mark.parametrize("n,depth,algo,dist", [
-    (8192, 1, "classic", "normal_scaled"),     # BASELINE config 2
+    (8192, 1, "classic", "normal_scaled"),     # the 8192^3 configuration
     (8192, 1, "winograd", "normal_scaled"),
-    (16384, 2, "classic", "uniform"),          # BASELINE config 3
+    (16384, 2, "classic", "uniform"),          # the 16384^3 configuration
     (16384, 0, "dense", "uniform"),
 ])
 def test_full_size_probe_vector_and_cublas(ops, n, depth, algo, dist):
