@@ -207,7 +207,7 @@ int b200s_combine(const b200s_problem* p, const void* products_device, void* C_d
  * dimension p->ldc. Destinations may be memory of other GPUs mapped into this process (peer or
  * symmetric memory): the stores are plain global stores, so a row-sharded product lands in every
  * GPU's copy of C without a separate all-gather. beta must be 0 and batch 1. The reference has no
- * multi-GPU product; this carries the exchange step of its north-star row-sharded configuration.
+ * multi-GPU product; this carries the exchange step of a row-sharded product.
  */
 int b200s_combine_peers(const b200s_problem* p, const void* products_device, void* const* C_list, int n_dst,
                         void* stream);

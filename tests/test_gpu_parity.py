@@ -346,7 +346,7 @@ def test_linear_under_autocast(ops):
     (16384, 0, "dense", "uniform"),
 ])
 def test_full_size_probe_vector_and_cublas(ops, n, depth, algo, dist):
-    """At BASELINE sizes the oracle is too slow; C is checked through C.x = A.(B.x) for random x
+    """At the full benchmark sizes the oracle is too slow; C is checked through C.x = A.(B.x) for random x
     in fp64 (linear in every entry of C) and against cuBLAS on the same inputs."""
     g = torch.Generator("cpu").manual_seed(0)
     if dist == "uniform":
