@@ -29,7 +29,7 @@ typedef enum b200s_status {
   B200S_ERR_BAD_ALIGNMENT = -4, /* base pointer not 16-byte aligned */
   B200S_ERR_BAD_DTYPE = -5,
   B200S_ERR_BAD_ALGO = -6,
-  B200S_ERR_BAD_DEPTH = -7,
+  B200S_ERR_BAD_DEPTH = -7,     /* depth outside 0..4 (b200s_preadd / b200s_combine / b200s_matmul_static: 1..2) */
   B200S_ERR_WORKSPACE_TOO_SMALL = -8,
   B200S_ERR_CUDA = -9,          /* a CUDA runtime/driver call failed; see b200s_last_cuda_error */
   B200S_ERR_NO_DEVICE = -10,    /* no sm_100 device is current */
@@ -79,7 +79,10 @@ typedef struct b200s_problem {
   int32_t in_dtype;   /* b200s_dtype of A and B */
   int32_t out_dtype;  /* b200s_dtype of C */
   int32_t algo;       /* b200s_algo */
-  int32_t depth;      /* recursion levels 0..2, or -1 = tuner table decides */
+  int32_t depth;      /* recursion levels 0..4, or -1 = tuner table decides. Up to two levels run as one
+                         pre-add / grouped GEMM / recombination pipeline; levels beyond that wrap it in
+                         host-side recursion (one outer level around seven products of one level less,
+                         operand sums rounded at each outer level as in the reference's recursion) */
   int32_t beta;       /* 0: C = A.B   1: C += A.B */
   int32_t prod_dtype; /* dtype the 7^depth sub-products are stored in between the GEMM and the
                          recombination: B200S_FP32, or the input dtype (the reference's rounding

@@ -87,6 +87,10 @@ bool valid_dtype(int d) { return d == B200S_BF16 || d == B200S_FP16 || d == B200
 
 // Largest depth <= want for which every extent splits into 2^depth blocks whose contiguous
 // runs are whole 16-byte vectors.
+// Levels beyond two run as host-side recursion: one outer level of pre-addition and recombination
+// around seven products of one level less (see run_deep).
+constexpr int kMaxDepth = 4;
+
 int feasible_depth(const b200s_problem& p, int want) {
   int d = want;
   while (d > 0) {
@@ -104,6 +108,7 @@ struct Plan {
   size_t sa_bytes, sb_bytes, mp_bytes;
   size_t ta_bytes, tb_bytes;  // K-major copies of fp32 operands given MN-major
   size_t a3_bytes, b3_bytes;  // hi/lo split operands of the three-pass TF32 mode
+  size_t deep_bytes;          // scratch of the recursion for more than two levels
   bool split3;
   size_t total_bytes;
 };
@@ -117,7 +122,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   if (p->a_major != B200S_K_MAJOR && p->a_major != B200S_MN_MAJOR) return B200S_ERR_BAD_STRIDE;
   if (p->b_major != B200S_K_MAJOR && p->b_major != B200S_MN_MAJOR) return B200S_ERR_BAD_STRIDE;
   if (p->algo < B200S_ALGO_AUTO || p->algo > B200S_ALGO_WINOGRAD) return B200S_ERR_BAD_ALGO;
-  if (p->depth < -1 || p->depth > 2) return B200S_ERR_BAD_DEPTH;
+  if (p->depth < -1 || p->depth > kMaxDepth) return B200S_ERR_BAD_DEPTH;
   if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
   if (p->pipeline < 0 || p->pipeline > 2) return B200S_ERR_BAD_SHAPE;
   if (p->precision != B200S_PREC_TF32 && p->precision != B200S_PREC_3XTF32) return B200S_ERR_BAD_DTYPE;
@@ -174,6 +179,37 @@ int make_plan(const b200s_problem* p, Plan* plan) {
     const size_t nb3 = static_cast<size_t>(p->batch) * static_cast<size_t>(plan->np);
     plan->a3_bytes = round256(nb3 * plan->Mb * plan->Kb * 3 * 4);
     plan->b3_bytes = round256(nb3 * plan->Nb * plan->Kb * 3 * 4);
+  }
+  plan->deep_bytes = 0;
+  if (depth > 2) {
+    if (p->batch != 1) return B200S_ERR_BAD_SHAPE;
+    // scratch of every outer level (7 operand blocks of each side, 7 products) plus the scratch of
+    // one two-level product of the innermost extents, reused by all sub-products in turn
+    const size_t es3 = dtype_size(p->in_dtype), ps3 = dtype_size(pd);
+    size_t total = 0;
+    int64_t m = p->M, n = p->N, k = p->K;
+    for (int d = depth; d > 2; --d) {
+      m /= 2, n /= 2, k /= 2;
+      total += round256(7 * m * k * es3) + round256(7 * k * n * es3) + round256(7 * m * n * ps3);
+    }
+    b200s_problem inner = *p;
+    inner.M = m, inner.N = n, inner.K = k;
+    inner.a_major = inner.b_major = B200S_K_MAJOR;  // extents only matter here
+    inner.lda = k, inner.ldb = k, inner.ldc = n;
+    if (p->in_dtype != B200S_FP32) {
+      inner.a_major = p->a_major, inner.b_major = p->b_major;
+      inner.lda = p->a_major == B200S_K_MAJOR ? k : m;
+      inner.ldb = p->b_major == B200S_K_MAJOR ? k : n;
+    }
+    inner.algo = algo, inner.depth = 2, inner.out_dtype = pd, inner.beta = 0;
+    Plan ip;
+    int rc = make_plan(&inner, &ip);
+    if (rc) return rc;
+    plan->deep_bytes = total + ip.total_bytes;
+    plan->a3_bytes = plan->b3_bytes = 0;
+    plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = 0;
+    plan->total_bytes = plan->ta_bytes + plan->tb_bytes + plan->deep_bytes;
+    return B200S_OK;
   }
   if (depth == 0) {
     plan->sa_bytes = plan->sb_bytes = plan->mp_bytes = 0;
@@ -299,6 +335,51 @@ int run_pipelined(const b200s_problem* p, const Plan& plan, const void* A, const
   return B200S_OK;
 }
 
+// More than two levels: one outer level here (operand sums rounded to the operand dtype, as the
+// reference's recursion rounds S1..S10 at every level, fixed_strassen_fp32_agg.py:87-96), seven
+// products of one level less through b200s_matmul, one outer recombination in fp32.
+int run_deep(const b200s_problem* p, const Plan& plan, const void* A, const void* B, void* C, uint8_t* ws,
+             cudaStream_t stream) {
+  const size_t es = dtype_size(p->in_dtype), ps = dtype_size(plan.prod_dtype);
+  const int64_t Mb = p->M / 2, Nb = p->N / 2, Kb = p->K / 2;
+  const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+  uint8_t* Sa = ws;
+  uint8_t* Sb = Sa + round256(7 * Mb * Kb * es);
+  uint8_t* Mp = Sb + round256(7 * Kb * Nb * es);
+  uint8_t* inner = Mp + round256(7 * Mb * Nb * ps);
+
+  PreaddArgs pa;
+  pa.batch = 1, pa.strideX = 0, pa.algo = plan.algo, pa.depth = 1, pa.dtype = p->in_dtype;
+  pa.X = A, pa.out = Sa, pa.side = 0;
+  pa.rows_blk = a_k ? Mb : Kb, pa.cols_blk = a_k ? Kb : Mb, pa.ld = p->lda, pa.transposed = !a_k;
+  int rc = launch_preadd(pa, stream);
+  if (rc) return rc;
+  pa.X = B, pa.out = Sb, pa.side = 1;
+  pa.rows_blk = b_k ? Nb : Kb, pa.cols_blk = b_k ? Kb : Nb, pa.ld = p->ldb, pa.transposed = b_k;
+  rc = launch_preadd(pa, stream);
+  if (rc) return rc;
+
+  b200s_problem q = *p;
+  q.M = Mb, q.N = Nb, q.K = Kb, q.batch = 1;
+  q.lda = a_k ? Kb : Mb, q.ldb = b_k ? Kb : Nb, q.ldc = Nb;
+  q.strideA = q.strideB = q.strideC = 0;
+  q.algo = plan.algo, q.depth = plan.depth - 1;
+  q.out_dtype = plan.prod_dtype, q.beta = 0, q.pipeline = 2, q.b_blocks_ready = 0;
+  size_t need = 0;
+  rc = b200s_workspace_bytes(&q, &need);
+  if (rc) return rc;
+  for (int i = 0; i < 7; ++i) {
+    rc = b200s_matmul(&q, Sa + static_cast<size_t>(i) * Mb * Kb * es, Sb + static_cast<size_t>(i) * Kb * Nb * es,
+                      Mp + static_cast<size_t>(i) * Mb * Nb * ps, inner, need, stream);
+    if (rc) return rc;
+  }
+  CombineArgs c;
+  c.products = Mp, c.C = C;
+  c.Mb = Mb, c.Nb = Nb, c.ldc = p->ldc, c.batch = 1, c.strideC = 0;
+  c.algo = plan.algo, c.depth = 1, c.prod_dtype = plan.prod_dtype, c.out_dtype = p->out_dtype, c.beta = p->beta;
+  return launch_combine(c, stream);
+}
+
 }  // namespace
 
 void note_cuda_error(cudaError_t e, const char* where) {
@@ -332,7 +413,7 @@ const char* b200s_status_string(int status) {
     case B200S_ERR_BAD_ALIGNMENT: return "base pointer not 16-byte aligned";
     case B200S_ERR_BAD_DTYPE: return "unsupported dtype";
     case B200S_ERR_BAD_ALGO: return "unknown algorithm";
-    case B200S_ERR_BAD_DEPTH: return "depth out of range (0..2, or -1 for the tuner table)";
+    case B200S_ERR_BAD_DEPTH: return "depth out of range (0..4, or -1 for the tuner table)";
     case B200S_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
     case B200S_ERR_CUDA: return "CUDA call failed";
     case B200S_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
@@ -481,6 +562,8 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
     p->b_major = B200S_K_MAJOR, p->ldb = p->K, p->strideB = p->K * p->N;
   }
 
+  if (plan.depth > 2) return run_deep(p, plan, A, B, C, ws + plan.ta_bytes + plan.tb_bytes, stream);
+
   GemmArgs g;
   g.cta_group = p->tile_variant;
   if (g.cta_group < 0 || g.cta_group > 3) return B200S_ERR_BAD_SHAPE;
@@ -611,6 +694,7 @@ int b200s_matmul_static(const b200s_problem* p_in, const void* A, const void* B,
   Plan plan;
   int rc = make_plan(p_in, &plan);
   if (rc) return rc;
+  if (plan.depth > 2) return B200S_ERR_BAD_DEPTH;  // the recursion for deeper levels is not offered here
   if (plan.total_bytes > kStaticScratchBytes) return B200S_ERR_TOO_LARGE;
   StaticState* st = nullptr;
   rc = static_state(&st);
@@ -713,7 +797,7 @@ int b200s_tuner_record(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_
   if (M <= 0 || N <= 0 || K <= 0) return B200S_ERR_BAD_SHAPE;
   if (!valid_dtype(in_dtype)) return B200S_ERR_BAD_DTYPE;
   if (algo < B200S_ALGO_DENSE || algo > B200S_ALGO_WINOGRAD) return B200S_ERR_BAD_ALGO;
-  if (depth < 0 || depth > 2) return B200S_ERR_BAD_DEPTH;
+  if (depth < 0 || depth > kMaxDepth) return B200S_ERR_BAD_DEPTH;
   if (algo == B200S_ALGO_DENSE) depth = 0;
   std::lock_guard<std::mutex> lock(g_tuner_mu);
   for (auto& e : g_tuner) {
@@ -763,7 +847,7 @@ int b200s_tuner_load(const char* path) {
     int dt, algo, depth;
     if (std::sscanf(line, "%lld %lld %lld %d %d %d", &m, &n, &k, &dt, &algo, &depth) != 6 || m <= 0 || n <= 0 ||
         k <= 0 || !valid_dtype(dt) || algo < B200S_ALGO_DENSE || algo > B200S_ALGO_WINOGRAD || depth < 0 ||
-        depth > 2) {
+        depth > kMaxDepth) {
       bad = true;
       break;
     }

@@ -20,7 +20,7 @@ import torch
 
 from . import ops
 
-MAX_DEPTH = 2  # levels the CUDA library unrolls; deeper requests run two levels
+MAX_DEPTH = 4  # levels the CUDA library accepts; deeper requests run four levels
 
 
 def _accumulate(A, B, C, algo, depth):

@@ -51,7 +51,7 @@ class LinearStrassen(nn.Linear):
         elif self.depth == 0:
             algo, depth = "dense", 0
         else:
-            algo, depth = self.algo, min(self.depth, 2)
+            algo, depth = self.algo, min(self.depth, 4)
             # sizes that do not split into whole 16-byte vectors use fewer levels
             while depth > 0 and any(v % (8 << depth) for v in (x.shape[0], d_in, self.out_features)):
                 depth -= 1

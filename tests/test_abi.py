@@ -66,6 +66,9 @@ def test_workspace_layout(lib):
     assert rc == 0 and n == 2 * 7 * 512 * 512 * 2 + 7 * 512 * 512 * 4
     rc, n = ws_bytes(lib, problem(algo=_lib.ALGO_DENSE))
     assert rc == 0 and n == 0
+    # three levels: one outer level (7 blocks of 512^2 per side and 7 products) around a two-level 512^3 product
+    rc, n = ws_bytes(lib, problem(depth=3))
+    assert rc == 0 and n == 3 * 7 * 512 * 512 * 2 + 3 * 49 * 128 * 128 * 2
 
 
 @pytest.mark.parametrize("kw,status", [
@@ -73,7 +76,7 @@ def test_workspace_layout(lib):
     (dict(M=1000), _lib.ERR_BAD_SHAPE),            # 1000 is not a multiple of 4 * 8
     (dict(in_dtype=7), _lib.ERR_BAD_DTYPE),
     (dict(algo=9), _lib.ERR_BAD_ALGO),
-    (dict(depth=3), _lib.ERR_BAD_DEPTH),
+    (dict(depth=5), _lib.ERR_BAD_DEPTH),
     (dict(lda=512), _lib.ERR_BAD_STRIDE),
     (dict(beta=2), _lib.ERR_BAD_SHAPE),
 ])
