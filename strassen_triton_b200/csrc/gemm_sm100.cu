@@ -320,6 +320,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         ((p.strideC * out_es) % 16 == 0);
     const uint32_t stg = staging_base + static_cast<uint32_t>(ew * STG_BUFS) * 4096u;
     const uint32_t sw = static_cast<uint32_t>(lane & 7);
+    // C is not read again by this kernel: let its lines leave L2 before the operand tiles do
+    const uint64_t store_policy = ptx::make_evict_first_policy();
     int it = 0;
     int stage_flip = 0;
     for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it) {
@@ -364,7 +366,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_3d(&tmC, sbuf, col0 + gc, row_warp, b);
+          ptx::tma_store_3d_hint(&tmC, sbuf, col0 + gc, row_warp, b, store_policy);
           ptx::tma_store_commit();
         }
         if constexpr (STG_BUFS == 2) stage_flip ^= 1;
