@@ -300,15 +300,6 @@ def run_gpu_arm(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
-    # cuBLAS dense bf16 on the same GPU and inputs, same timing protocol, half of it before and half
-    # after the timed region so that neither side always runs on the warmer GPU
-    dense_ms = []
-    if world == 1:
-        dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
-        for _ in range(3):
-            dense()
-        dense_ms.append(timed(dense, max(1, args.steps // 2), sync, barrier) / max(1, args.steps // 2))
-        step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -359,6 +350,13 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = t.item()
     e2e_value = flops * e2e_steps / (ms_e2e * 1e-3) / 1e12
+    ms_dense = None
+    if world == 1:
+        # cuBLAS dense bf16 on the same GPU and inputs, same timing protocol as `value`
+        dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
+        for _ in range(max(args.warmup, 3)):
+            dense()
+        ms_dense = timed(dense, args.steps, sync, barrier) / args.steps
     h2d = (hA.numel() + hB.numel()) * 2
     d2h = hC.numel() * 2
 
@@ -402,11 +400,10 @@ def run_gpu_arm(args):
                 "preadd_B_gbs": round(pre_bytes / (stages["preadd_B"] * 1e-3) / 1e9, 1),
                 "combine_gbs": round(comb_bytes / (stages["combine"] * 1e-3) / 1e9, 1),
                 "hbm_peak_gbs": hbm, "peak_kind": f"copy bandwidth, of {peaks['source']}"}
-            dense_ms.append(timed(dense, max(1, args.steps // 2), sync, barrier) / max(1, args.steps // 2))
-            ms_dense = sum(dense_ms) / len(dense_ms)
             line["cublas_dense"] = {"value": round(flops / (ms_dense * 1e-3) / 1e12, 2), "unit": UNIT,
                                     "ms_per_step": round(ms_dense, 4),
-                                    "ms_before_and_after": [round(x, 4) for x in dense_ms]}
+                                    "protocol": "same steps and warm-up as `value`, started after the PCIe-bound "
+                                                "end-to-end phase so that both start on an equally rested GPU"}
             line["cpu_baseline"] = cpu_baseline()
     if world > 1:
         dist.barrier()
