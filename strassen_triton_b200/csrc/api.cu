@@ -69,9 +69,9 @@ double log_volume(int64_t M, int64_t N, int64_t K) {
 }
 
 // Built-in choice when the table holds nothing for the dtype: a dense product below a cube of
-// kDefaultCrossover, two Strassen levels from there on (measured on B200, bf16: at 8192^3 the dense
-// kernel wins, at 16384^3 and 32768^3 two levels win over one level and over dense).
-constexpr int64_t kDefaultCrossover = 12288;
+// kDefaultCrossover, two Strassen levels from there on (measured on B200, bf16: up to 12288^3 the
+// dense kernel wins, at 16384^3 and 32768^3 two levels win over one level and over dense).
+constexpr int64_t kDefaultCrossover = 14336;
 
 void default_choice(int64_t M, int64_t N, int64_t K, int32_t* algo, int32_t* depth) {
   const double v = log_volume(M, N, K);

@@ -21,17 +21,21 @@ _DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float32: _lib.
 
 
 def _time(fn, reps: int) -> float:
-    for _ in range(2):
+    """Milliseconds per call over `reps` back-to-back calls (CUDA events around the whole run), best
+    of three such runs after warm-up: the regime of a training loop or of bench.py, where host-side
+    launch work is hidden behind the previous call."""
+    for _ in range(3):
         fn()
     torch.cuda.synchronize()
     best = float("inf")
-    for _ in range(reps):
+    for _ in range(3):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        best = min(best, e0.elapsed_time(e1))
+        best = min(best, e0.elapsed_time(e1) / reps)
     return best
 
 
