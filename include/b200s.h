@@ -97,6 +97,14 @@ typedef struct b200s_problem {
   int32_t b_blocks_ready; /* 1: the operand blocks of B already sit in `workspace` from an earlier call with
                          the same B, extents, dtype, algo, depth and schedule (and the same workspace):
                          skip forming them. Used when one B multiplies several row panels of A. */
+  int32_t fuse;       /* whether the operand sums and the recombination run inside the product kernel:
+                         0 = library decides, 1 = fused (one persistent kernel multiplies all 7^depth blocks
+                         while extra warps of every CTA form the later groups' operand blocks and recombine
+                         each quadrant of C as soon as its products are stored), 2 = separate passes (then
+                         `pipeline` picks their schedule), 3 = fused, but the last quadrant of C is
+                         recombined by a full-width launch after the kernel. Fused needs batch 1, depth 1-2,
+                         16-bit operands with prod_dtype equal to them, tile_variant 0 or 3; an explicit
+                         1 or 3 that cannot be met returns B200S_ERR_BAD_SHAPE */
 } b200s_problem;
 
 /* Library version, major*10000 + minor*100 + patch. */

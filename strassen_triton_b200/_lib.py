@@ -47,7 +47,7 @@ class Problem(ctypes.Structure):
         ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
         ("algo", ctypes.c_int32), ("depth", ctypes.c_int32), ("beta", ctypes.c_int32),
         ("prod_dtype", ctypes.c_int32), ("precision", ctypes.c_int32), ("tile_variant", ctypes.c_int32),
-        ("pipeline", ctypes.c_int32), ("b_blocks_ready", ctypes.c_int32),
+        ("pipeline", ctypes.c_int32), ("b_blocks_ready", ctypes.c_int32), ("fuse", ctypes.c_int32),
     ]
 
 

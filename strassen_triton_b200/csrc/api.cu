@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -109,9 +110,14 @@ struct Plan {
   size_t ta_bytes, tb_bytes;  // K-major copies of fp32 operands given MN-major
   size_t a3_bytes, b3_bytes;  // hi/lo split operands of the three-pass TF32 mode
   size_t deep_bytes;          // scratch of the recursion for more than two levels
+  size_t flag_bytes;          // counters the CTAs of the fused kernel share (last bytes of the scratch)
   bool split3;
   size_t total_bytes;
 };
+
+constexpr size_t kFlagBytes = 256;
+// Smallest cube edge from which the library picks the fused schedule on its own.
+constexpr double kFusedFrom = 2048.0;
 
 size_t round256(size_t x) { return (x + 255) & ~size_t{255}; }
 
@@ -125,6 +131,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   if (p->depth < -1 || p->depth > kMaxDepth) return B200S_ERR_BAD_DEPTH;
   if (p->beta != 0 && p->beta != 1) return B200S_ERR_BAD_SHAPE;
   if (p->pipeline < 0 || p->pipeline > 2) return B200S_ERR_BAD_SHAPE;
+  if (p->fuse < 0 || p->fuse > 3) return B200S_ERR_BAD_SHAPE;
   if (p->precision != B200S_PREC_TF32 && p->precision != B200S_PREC_3XTF32) return B200S_ERR_BAD_DTYPE;
   if (p->b_blocks_ready != 0 && p->b_blocks_ready != 1) return B200S_ERR_BAD_SHAPE;
   const int64_t a_cols = p->a_major == B200S_K_MAJOR ? p->K : p->M;
@@ -181,6 +188,7 @@ int make_plan(const b200s_problem* p, Plan* plan) {
     plan->b3_bytes = round256(nb3 * plan->Nb * plan->Kb * 3 * 4);
   }
   plan->deep_bytes = 0;
+  plan->flag_bytes = 0;
   if (depth > 2) {
     if (p->batch != 1) return B200S_ERR_BAD_SHAPE;
     // scratch of every outer level (7 operand blocks of each side, 7 products) plus the scratch of
@@ -221,8 +229,9 @@ int make_plan(const b200s_problem* p, Plan* plan) {
   plan->sa_bytes = round256(nb * plan->Mb * plan->Kb * es);
   plan->sb_bytes = round256(nb * plan->Kb * plan->Nb * es);
   plan->mp_bytes = round256(nb * plan->Mb * plan->Nb * ps);
+  plan->flag_bytes = kFlagBytes;
   plan->total_bytes = plan->sa_bytes + plan->sb_bytes + plan->mp_bytes + plan->ta_bytes + plan->tb_bytes +
-                      plan->a3_bytes + plan->b3_bytes;
+                      plan->a3_bytes + plan->b3_bytes + plan->flag_bytes;
   return B200S_OK;
 }
 
@@ -332,6 +341,122 @@ int run_pipelined(const b200s_problem* p, const Plan& plan, const void* A, const
   }
   B200S_CUDA_OK(cudaEventRecord(ds->ev_end, ds->s_add));
   B200S_CUDA_OK(cudaStreamWaitEvent(user, ds->ev_end, 0));
+  return B200S_OK;
+}
+
+// Can the fused kernel carry this product? One product (no batch), one or two levels, 16-bit operands
+// with the products stored in the same type, 256 x 512 tiles, blocks small enough for 32-bit positions.
+bool fused_eligible(const b200s_problem* p, const Plan& plan) {
+  if (p->batch != 1 || plan.depth < 1 || plan.depth > 2 || plan.split3) return false;
+  if (p->in_dtype != B200S_BF16 && p->in_dtype != B200S_FP16) return false;
+  if (plan.prod_dtype != p->in_dtype) return false;
+  if (p->tile_variant != 0 && p->tile_variant != 3) return false;
+  const int64_t lim = int64_t{1} << 31;
+  return plan.Mb * plan.Kb / 8 < lim && plan.Kb * plan.Nb / 8 < lim && plan.Mb * plan.Nb / 8 < lim;
+}
+
+// Strassen as one persistent launch (launch_fused): the operand blocks of the first outer group are
+// formed by the stand-alone pass, then the fused kernel multiplies all groups while its adder warps
+// form the later groups' blocks and recombine every quadrant of C whose groups are done. With
+// tail_outside the quadrant(s) that need the last group are left to a full-width recombination
+// launch after the kernel instead of to the adder warps.
+int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const void* B, void* C, void* Sa, void* Sb,
+              void* Mp, uint32_t* flags, bool tail_outside, cudaStream_t stream) {
+  const bool wino = plan.algo == B200S_ALGO_WINOGRAD;
+  const int* order = wino ? kOrderWinograd : kOrderClassic;
+  const int sa = wino ? sched::kWinograd : sched::kClassic;
+  const int np2 = static_cast<int>(plan.np / 7);
+  int pos[7];
+  for (int i = 0; i < 7; ++i) pos[order[i]] = i;
+  const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+
+#ifdef B200S_FUSED_TRACE
+  // development build: the kernel leaves timestamps of CTA 0 behind the counters (the scratch is
+  // then over-allocated by the caller); environment switches take work out of the kernel
+  B200S_CUDA_OK(cudaMemsetAsync(flags, 0, 64, stream));
+  const char* dbg_env = std::getenv("B200S_FUSED_DEBUG");
+  const int dbg = dbg_env ? std::atoi(dbg_env) : 0;
+#else
+  B200S_CUDA_OK(cudaMemsetAsync(flags, 0, 64, stream));
+  const int dbg = 0;
+#endif
+
+  PreaddOuterArgs pa;
+  pa.batch = 1, pa.strideX = 0;
+  pa.algo = plan.algo, pa.depth = plan.depth, pa.dtype = p->in_dtype;
+  pa.n_groups = 1;
+  pa.groups[0] = order[0];
+  pa.out_block0[0] = 0;
+  pa.X = A, pa.out = Sa, pa.side = 0;
+  pa.rows_blk = a_k ? plan.Mb : plan.Kb, pa.cols_blk = a_k ? plan.Kb : plan.Mb;
+  pa.ld = p->lda, pa.transposed = !a_k;
+  int rc = launch_preadd_outer(pa, stream);
+  if (rc) return rc;
+  PreaddOuterArgs pb = pa;
+  pb.X = B, pb.out = Sb, pb.side = 1;
+  pb.rows_blk = b_k ? plan.Nb : plan.Kb, pb.cols_blk = b_k ? plan.Kb : plan.Nb;
+  pb.ld = p->ldb, pb.transposed = b_k;
+  if (!p->b_blocks_ready) {
+    rc = launch_preadd_outer(pb, stream);
+    if (rc) return rc;
+  }
+  int formed = 1;
+  if (dbg & 1) {
+    // every group formed before the kernel
+    for (int i = 1; i < 7; ++i) {
+      pa.groups[0] = order[i], pa.out_block0[0] = i * np2;
+      pb.groups[0] = order[i], pb.out_block0[0] = i * np2;
+      rc = launch_preadd_outer(pa, stream);
+      if (rc) return rc;
+      if (!p->b_blocks_ready) rc = launch_preadd_outer(pb, stream);
+      if (rc) return rc;
+    }
+    formed = 7;
+  }
+
+  int last_pos[4], tail_mask = 0;
+  for (int r = 0; r < 4; ++r) {
+    last_pos[r] = 0;
+    for (int p1 = 0; p1 < 7; ++p1)
+      if (sched::w1(sa, r, p1) != 0 && pos[p1] > last_pos[r]) last_pos[r] = pos[p1];
+    if ((tail_outside && last_pos[r] == 6) || (dbg & 2)) tail_mask |= 1 << r;
+  }
+
+  FusedArgs f;
+  GemmArgs& g = f.gemm;
+  g.cta_group = 3;
+  g.in_dtype = p->in_dtype, g.a_major = p->a_major, g.b_major = p->b_major;
+  g.A = Sa, g.B = Sb, g.C = Mp;
+  g.M = plan.Mb, g.N = plan.Nb, g.K = plan.Kb, g.batch = plan.np;
+  g.lda = a_k ? plan.Kb : plan.Mb, g.ldb = b_k ? plan.Kb : plan.Nb, g.ldc = plan.Nb;
+  g.strideA = plan.Mb * plan.Kb, g.strideB = plan.Kb * plan.Nb, g.strideC = plan.Mb * plan.Nb;
+  g.out_dtype = plan.prod_dtype, g.beta = 0;
+  f.algo = plan.algo, f.depth = plan.depth;
+  f.A = A, f.B = B, f.lda = p->lda, f.ldb = p->ldb;
+  f.a_rows_blk = pa.rows_blk, f.a_cols_blk = pa.cols_blk, f.a_transposed = pa.transposed;
+  f.b_rows_blk = pb.rows_blk, f.b_cols_blk = pb.cols_blk, f.b_transposed = pb.transposed;
+  f.C = C, f.Mb = plan.Mb, f.Nb = plan.Nb, f.ldc = p->ldc, f.out_dtype = p->out_dtype, f.beta = p->beta;
+  for (int i = 0; i < 7; ++i) f.order[i] = order[i];
+  f.groups_formed = formed;
+  f.b_formed = p->b_blocks_ready ? 1 : 0;
+  f.quads_inside = 0xf & ~tail_mask;
+  f.flags = flags;
+  rc = launch_fused(f, stream);
+  if (rc) return rc;
+
+  if (tail_mask) {
+    CombineOuterArgs ca;
+    ca.n_quads = 0;
+    for (int r = 0; r < 4; ++r)
+      if (tail_mask & (1 << r)) ca.quads[ca.n_quads++] = r;
+    ca.products = Mp, ca.C = C;
+    ca.Mb = plan.Mb, ca.Nb = plan.Nb, ca.ldc = p->ldc, ca.batch = 1, ca.strideC = 0;
+    ca.algo = plan.algo, ca.depth = plan.depth, ca.prod_dtype = plan.prod_dtype, ca.out_dtype = p->out_dtype;
+    ca.beta = p->beta;
+    for (int p1 = 0; p1 < 7; ++p1) ca.group_block0[p1] = pos[p1] * np2;
+    rc = launch_combine_outer(ca, stream);
+    if (rc) return rc;
+  }
   return B200S_OK;
 }
 
@@ -596,8 +721,17 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   void* Sb = ws + plan.sa_bytes;
   void* Mp = ws + plan.sa_bytes + plan.sb_bytes;
 
-  // Large single products run the pipelined driver unless the caller chose otherwise.
   const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
+  // The fused schedule: asked for (fuse 1 / 3), or the library's choice (fuse 0) for products from
+  // kFusedFrom^3 on when the caller left the schedule open.
+  if (p->fuse == 1 || p->fuse == 3 || (p->fuse == 0 && p->pipeline == 0 && volume >= kFusedFrom * kFusedFrom * kFusedFrom)) {
+    if (fused_eligible(p, plan)) {
+      uint32_t* flags = reinterpret_cast<uint32_t*>(ws + plan.total_bytes - plan.flag_bytes);
+      return run_fused(p, plan, A, B, C, Sa, Sb, Mp, flags, p->fuse == 3, stream);
+    }
+    if (p->fuse != 0) return B200S_ERR_BAD_SHAPE;  // an explicit request must be met
+  }
+  // Large single products run the pipelined driver unless the caller chose otherwise.
   const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 24576.0 * 24576.0 * 24576.0);
   if (p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 

@@ -10,13 +10,12 @@
 // base_dtype, vstack/hstack). With beta = 1 it adds into C as the reference's run_* launchers do
 // (strassen.py:184-192).
 
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <mutex>
 #include <utility>
 
+#include "combine_device.cuh"
 #include "common.h"
 #include "schedule.h"
 
@@ -24,161 +23,14 @@ namespace b200s {
 
 namespace {
 
+using namespace comb;
+
 struct CombineKernelParams {
   const void* products;
   void* C;
   int64_t Mb, nb_vec;  // block rows, 16-byte product vectors per block row
   int64_t ldc, strideC;
   int32_t out_dtype, beta, vec_ok;
-};
-
-template <typename T>
-struct PVec {
-  static constexpr int N = 16 / sizeof(T);
-};
-
-// 8-byte loads of four 16-bit products: the depth-2 single-pass kernel keeps 16 x 4 accumulators
-// instead of 16 x 8, which triples the resident threads and with them the loads in flight.
-__device__ __forceinline__ void load_pvec4(const __nv_bfloat16* ptr, float (&f)[4]) {
-  const uint2 v = __ldcs(reinterpret_cast<const uint2*>(ptr));
-  f[0] = __uint_as_float(v.x << 16), f[1] = __uint_as_float(v.x & 0xffff0000u);
-  f[2] = __uint_as_float(v.y << 16), f[3] = __uint_as_float(v.y & 0xffff0000u);
-}
-__device__ __forceinline__ void load_pvec4(const __half* ptr, float (&f)[4]) {
-  const uint2 v = __ldcs(reinterpret_cast<const uint2*>(ptr));
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
-}
-__device__ __forceinline__ void load_pvec4(const float* ptr, float (&f)[4]) {
-  const float4 v = __ldcs(reinterpret_cast<const float4*>(ptr));
-  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
-}
-
-template <typename T>
-__device__ __forceinline__ void load_pvec(const T* ptr, float (&f)[PVec<T>::N]);
-template <>
-__device__ __forceinline__ void load_pvec<float>(const float* ptr, float (&f)[4]) {
-  const float4 v = __ldcs(reinterpret_cast<const float4*>(ptr));
-  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
-}
-template <>
-__device__ __forceinline__ void load_pvec<__nv_bfloat16>(const __nv_bfloat16* ptr, float (&f)[8]) {
-  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(ptr));
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void load_pvec<__half>(const __half* ptr, float (&f)[8]) {
-  const uint4 v = __ldcs(reinterpret_cast<const uint4*>(ptr));
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    f[2 * i] = t.x, f[2 * i + 1] = t.y;
-  }
-}
-
-template <typename OutT>
-__device__ __forceinline__ OutT cvt(float v);
-template <>
-__device__ __forceinline__ float cvt<float>(float v) {
-  return v;
-}
-template <>
-__device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-template <>
-__device__ __forceinline__ __half cvt<__half>(float v) {
-  return __float2half_rn(v);
-}
-__device__ __forceinline__ float widen(float v) { return v; }
-__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
-__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
-
-// Writes N consecutive output elements, as 16-byte vectors when aligned.
-template <typename OutT, int N>
-__device__ __forceinline__ void store_out(OutT* dst, const float (&f)[N], bool beta, bool vec_ok) {
-  constexpr int kPer = 16 / sizeof(OutT);
-  if constexpr (N >= kPer) {
-    if (vec_ok) {
-#pragma unroll
-      for (int v = 0; v < N / kPer; ++v) {
-        union {
-          uint4 u;
-          OutT e[kPer];
-        } pack;
-        if (beta) {
-          pack.u = *reinterpret_cast<const uint4*>(dst + v * kPer);
-#pragma unroll
-          for (int i = 0; i < kPer; ++i) pack.e[i] = cvt<OutT>(widen(pack.e[i]) + f[v * kPer + i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < kPer; ++i) pack.e[i] = cvt<OutT>(f[v * kPer + i]);
-        }
-        *reinterpret_cast<uint4*>(dst + v * kPer) = pack.u;
-      }
-      return;
-    }
-  }
-  if constexpr (N * sizeof(OutT) == 8) {
-    if (vec_ok) {
-      union {
-        uint2 u;
-        OutT e[N];
-      } pack;
-      if (beta) {
-        pack.u = *reinterpret_cast<const uint2*>(dst);
-#pragma unroll
-        for (int i = 0; i < N; ++i) pack.e[i] = cvt<OutT>(widen(pack.e[i]) + f[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i) pack.e[i] = cvt<OutT>(f[i]);
-      }
-      *reinterpret_cast<uint2*>(dst) = pack.u;
-      return;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < N; ++i) dst[i] = cvt<OutT>(beta ? widen(dst[i]) + f[i] : f[i]);
-}
-
-template <int DEPTH, int ALGO, typename TP>
-struct Combine {
-  static constexpr int NQ = sched::ipow(4, DEPTH);
-  static constexpr int NP = sched::ipow(7, DEPTH);
-  static constexpr int VEC = DEPTH == 2 ? 4 : PVec<TP>::N;
-
-  template <int P, int R>
-  static __device__ __forceinline__ void add_term(const float (&x)[VEC], float (&acc)[NQ][VEC]) {
-    constexpr int c = sched::w(ALGO, DEPTH, R, P);
-    if constexpr (c != 0) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[R][i] = c > 0 ? acc[R][i] + x[i] : acc[R][i] - x[i];
-    }
-  }
-
-  template <int P, int... Rs>
-  static __device__ __forceinline__ void one_product(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
-                                                     std::integer_sequence<int, Rs...>) {
-    float x[VEC];
-    if constexpr (VEC == PVec<TP>::N)
-      load_pvec<TP>(prod0 + P * blk_elems, x);
-    else
-      load_pvec4(prod0 + P * blk_elems, x);
-    (add_term<P, Rs>(x, acc), ...);
-  }
-
-  template <int... Ps>
-  static __device__ __forceinline__ void all_products(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
-                                                      std::integer_sequence<int, Ps...>) {
-    (one_product<Ps>(prod0, blk_elems, acc, std::make_integer_sequence<int, NQ>{}), ...);
-  }
 };
 
 template <int DEPTH, int ALGO, typename TP>
@@ -344,76 +196,11 @@ int launch_peers_dtype(const CombineArgs& a, void* const* dst, int n_dst, cudaSt
 // One launch writes a few outer quadrants of C only, reading just the product groups that feed
 // them, so the pipelined driver can recombine a quadrant as soon as its last group is done.
 
-struct CombineOuterParams {
-  const void* products;
-  void* C;
-  int64_t Mb, nb_vec;       // finest block rows, 16-byte product vectors per finest block row
-  int64_t ldc, strideC;
-  int64_t batch_blocks;     // product blocks per batch item (7^depth)
-  int32_t out_dtype, beta, vec_ok;
-  int8_t quad[4];           // outer quadrant of each listed entry
-  int8_t coef[4][7];        // [listed entry][outer product p1]
-  int32_t group_block0[7];  // first product block of outer product p1
-};
-
 template <int INNER, int ALGO, typename TP>
 __global__ void __launch_bounds__(256, 3) combine_outer_kernel(const CombineOuterParams p) {
-  constexpr int VEC = PVec<TP>::N;
-  constexpr int NQ2 = INNER ? 4 : 1;
-  constexpr int NP2 = INNER ? 7 : 1;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= p.Mb * p.nb_vec) return;
-  const int64_t row = idx / p.nb_vec;
-  const int64_t cv = idx - row * p.nb_vec;
-  const int64_t Nb = p.nb_vec * VEC;
-  const int64_t blk_elems = p.Mb * Nb;
-  const int e = blockIdx.y;
-
-  float acc[NQ2][VEC];
-#pragma unroll
-  for (int r = 0; r < NQ2; ++r)
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[r][i] = 0.f;
-
-  const TP* prod = static_cast<const TP*>(p.products) + static_cast<int64_t>(blockIdx.z) * p.batch_blocks * blk_elems +
-                   row * Nb + cv * VEC;
-#pragma unroll 1
-  for (int p1 = 0; p1 < 7; ++p1) {
-    const int c = p.coef[e][p1];
-    if (c == 0) continue;
-    const TP* g0 = prod + static_cast<int64_t>(p.group_block0[p1]) * blk_elems;
-    if constexpr (INNER) {
-      float part[NQ2][VEC];
-#pragma unroll
-      for (int r = 0; r < NQ2; ++r)
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) part[r][i] = 0.f;
-      Combine<1, ALGO, TP>::all_products(g0, blk_elems, part, std::make_integer_sequence<int, NP2>{});
-#pragma unroll
-      for (int r = 0; r < NQ2; ++r)
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[r][i] = c > 0 ? acc[r][i] + part[r][i] : acc[r][i] - part[r][i];
-    } else {
-      float x[VEC];
-      load_pvec<TP>(g0, x);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[0][i] = c > 0 ? acc[0][i] + x[i] : acc[0][i] - x[i];
-    }
-  }
-
-  const int r1 = p.quad[e];
-#pragma unroll
-  for (int r2 = 0; r2 < NQ2; ++r2) {
-    const int br = INNER ? 2 * (r1 >> 1) + (r2 >> 1) : (r1 >> 1);
-    const int bc = INNER ? 2 * (r1 & 1) + (r2 & 1) : (r1 & 1);
-    const int64_t off = static_cast<int64_t>(blockIdx.z) * p.strideC + (br * p.Mb + row) * p.ldc + bc * Nb + cv * VEC;
-    if (p.out_dtype == B200S_BF16)
-      store_out<__nv_bfloat16, VEC>(static_cast<__nv_bfloat16*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
-    else if (p.out_dtype == B200S_FP16)
-      store_out<__half, VEC>(static_cast<__half*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
-    else
-      store_out<float, VEC>(static_cast<float*>(p.C) + off, acc[r2], p.beta != 0, p.vec_ok != 0);
-  }
+  outer_position<INNER, ALGO, TP>(p, blockIdx.y, blockIdx.z, idx);
 }
 
 template <int INNER, int ALGO, typename TP>
@@ -439,7 +226,7 @@ int launch_outer_one(const CombineOuterArgs& a, cudaStream_t stream) {
   for (int p1 = 0; p1 < 7; ++p1) kp.group_block0[p1] = a.group_block0[p1];
   const int64_t total = kp.Mb * kp.nb_vec;
   const int64_t blocks = (total + 255) / 256;
-  if (blocks > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
+  if (total > INT32_MAX || a.batch > 65535) return B200S_ERR_BAD_SHAPE;
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.n_quads), static_cast<unsigned>(a.batch));
   combine_outer_kernel<INNER, ALGO, TP><<<grid, 256, 0, stream>>>(kp);
   B200S_CUDA_OK(cudaGetLastError());

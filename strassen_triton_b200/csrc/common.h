@@ -48,6 +48,30 @@ struct GemmArgs {
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 
+// ---- fused Strassen kernel (gemm_sm100.cu) ------------------------------------------------
+// One persistent launch that runs the grouped product over all 7^depth operand blocks while four
+// extra warps per CTA ("adders") form the operand blocks of the later outer groups and recombine
+// each outer quadrant of C as soon as the groups feeding it are done. Groups are laid out in
+// scratch in processing order: group i holds outer product order[i] (7 blocks at two levels, 1 at one).
+struct FusedArgs {
+  GemmArgs gemm;             // A = operand blocks of A, B = those of B, C = product blocks, batch = 7^depth
+  int algo, depth;           // classic / winograd, 1 or 2 levels
+  const void* A;             // original operands and how their blocks are stored (as PreaddArgs)
+  const void* B;
+  int64_t lda, ldb;
+  int64_t a_rows_blk, a_cols_blk, b_rows_blk, b_cols_blk;
+  int a_transposed, b_transposed;
+  void* C;                   // result, row-major
+  int64_t Mb, Nb, ldc;
+  int out_dtype, beta;
+  int order[7];              // outer products in processing order
+  int groups_formed;         // leading groups whose operand blocks were formed before this launch (>= 1)
+  int b_formed;              // 1: every block of B is in place already
+  int quads_inside;          // bit r set: outer quadrant r of C is recombined by this launch
+  uint32_t* flags;           // 16 words, zero when the kernel starts: counters the CTAs share
+};
+int launch_fused(const FusedArgs& f, cudaStream_t stream);
+
 // ---- fp32 operand re-layout (transpose.cu) -----------------------------------------------
 // out[c][r] = in[r][c] for a rows x cols fp32 matrix per batch item.
 int launch_transpose_f32(const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,

@@ -23,11 +23,13 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 #include <mutex>
 
+#include "combine_device.cuh"
 #include "common.h"
+#include "preadd_device.cuh"
 #include "ptx_sm100.cuh"
+#include "schedule.h"
 
 namespace b200s {
 
@@ -46,13 +48,150 @@ struct GemmKernelParams {
   int32_t fmt;                // operand format field of the instruction descriptor
   int32_t out_dtype, beta;
   int32_t tma_store;          // 1: the epilogue stages tiles in shared memory and stores them with TMA
+  int32_t l2_a, l2_b;         // L2 policy of the operand loads (ptx::make_l2_policy kinds)
   int64_t ldc, strideC;
   void* C;
   uint32_t* status;
 };
 
 // Role codes stored in the abort word / device status when a wait runs out.
-enum : uint32_t { kWhoProducer = 1, kWhoMma = 2, kWhoMmaAcc = 3, kWhoEpilogue = 4 };
+enum : uint32_t {
+  kWhoProducer = 1,
+  kWhoMma = 2,
+  kWhoMmaAcc = 3,
+  kWhoEpilogue = 4,
+  kWhoProducerGroup = 5,  // fused kernel: the producer waiting for a group's operand blocks
+  kWhoAdder = 6           // fused kernel: an adder warp waiting for a group's products
+};
+
+// ---- fused Strassen kernel: what the adder warps do ----------------------------------------------
+// Phase 1: the operand blocks of every outer group still to be formed, in processing order; warps 0-1
+// of the adder warpgroup take side A, warps 2-3 side B (all four side A when B's blocks exist already).
+// Phase 2: the quadrants of C, each once the groups feeding it are stored. Every CTA takes the
+// positions first, first + stride, ... of every task. The two sides and the two phases are separate
+// loops on purpose: the compiler then allocates registers for one body at a time.
+constexpr int kAdderThreads = 128;
+
+struct FusedKernelParams {
+  pre::PreaddOuterParams pre[2];  // listed group i = group at processing position i
+  comb::CombineOuterParams comb;  // listed entry e = outer quadrant e
+  uint32_t* flags;                // [0, 8): adder teams done with the operand blocks of group i; [8, 16): epilogue
+                                  // warps done with a tile of group i
+  uint32_t ready_target;          // value of a ready counter once every team of every CTA has signalled
+  uint32_t done_target;           // value of a done counter once every tile of a group is stored
+  int32_t np2;                    // product blocks per outer group
+  int32_t groups_formed;          // leading groups whose operand blocks existed before the launch
+  int32_t b_formed;               // all of B's blocks existed before the launch
+  int32_t n_comb;                 // quadrants of C recombined by the adders
+  int8_t comb_quad[4];            // in the order in which their groups complete
+  int8_t comb_wait[4];            // leading groups whose products the quadrant needs
+};
+
+struct NoFuse {
+  static constexpr bool kOn = false;
+  struct Params {};
+};
+template <int INNER, int ALGO, typename T>
+struct Fuse {
+  static constexpr bool kOn = true;
+  static constexpr int kInner = INNER, kAlgo = ALGO;
+  using Elem = T;
+  using Params = FusedKernelParams;
+};
+
+// The adders' loads and stores carry an evict-first L2 policy: what they stream through once must not
+// push the operand tiles of the products out of L2.
+template <int INNER, int ALGO, int SIDE, typename T>
+__device__ __forceinline__ void adder_preadd(const pre::PreaddOuterParams& p, int g, int64_t first, int64_t stride) {
+  using OP = pre::OuterPosition<INNER, ALGO, SIDE, T>;
+  const int64_t total = p.rows_blk * p.cols_vec;
+  const mem::Streaming access = mem::make_streaming();
+#pragma unroll 1
+  for (int64_t idx = first; idx < total; idx += stride) {
+    const typename OP::Where w = OP::locate(p, idx);
+    typename OP::Raw raw;
+    float t[OP::NQ2][OP::VEC];
+    OP::fetch(p, g, 0, w, raw, access);
+    OP::reduce(p, g, raw, t);
+    OP::store(p, g, 0, w, t, access);
+  }
+}
+
+template <int INNER, int ALGO, typename TP>
+__device__ __forceinline__ void adder_combine(const comb::CombineOuterParams& p, int e, int64_t first, int64_t stride) {
+  const int64_t total = p.Mb * p.nb_vec;
+  const mem::Streaming access = mem::make_streaming();
+#pragma unroll 1
+  for (int64_t idx = first; idx < total; idx += stride) comb::outer_position<INNER, ALGO, TP>(p, e, 0, idx, access);
+}
+
+// A team of `nthreads` adder threads (barrier `bar`) finished the operand blocks of group i: the blocks
+// will be read by TMA loads of other CTAs.
+__device__ __forceinline__ void adder_signal(uint32_t* ready, uint32_t bar, uint32_t nthreads, bool leader) {
+  ptx::fence_proxy_async_all();
+  ptx::named_bar_sync(bar, nthreads);
+  if (leader) {
+    __threadfence();
+    ptx::red_release_gpu_add(ready, 1u);
+  }
+}
+
+template <class F>
+__device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile uint32_t* abort_word, int tid) {
+  constexpr int INNER = F::kInner, ALGO = F::kAlgo;
+  using T = typename F::Elem;
+#ifdef B200S_FUSED_TRACE
+  const uint64_t trace_t0 = ptx::global_timer_ns();
+  const bool tracer = blockIdx.x == 0 && (tid & 63) == 0;
+#endif
+  // ---- phase 1: operand blocks
+  if (fz.b_formed || tid < 64) {
+    const int team = fz.b_formed ? kAdderThreads : 64;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * team + tid;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * team;
+#pragma unroll 1
+    for (int i = fz.groups_formed; i < 7; ++i) {
+      adder_preadd<INNER, ALGO, sched::kSideA, T>(fz.pre[0], i, first, stride);
+      adder_signal(fz.flags + i, 2, team, tid == 0);
+#ifdef B200S_FUSED_TRACE
+      if (tracer) fz.flags[64 + i] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
+#endif
+    }
+  } else {
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * 64 + (tid - 64);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 64;
+#pragma unroll 1
+    for (int i = fz.groups_formed; i < 7; ++i) {
+      adder_preadd<INNER, ALGO, sched::kSideB, T>(fz.pre[1], i, first, stride);
+      adder_signal(fz.flags + i, 3, 64, tid == 64);
+#ifdef B200S_FUSED_TRACE
+      if (tracer) fz.flags[72 + i] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
+#endif
+    }
+  }
+  // ---- phase 2: quadrants of C
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * kAdderThreads + tid;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kAdderThreads;
+#pragma unroll 1
+  for (int t = 0; t < fz.n_comb; ++t) {
+    // the products of the first comb_wait[t] groups must all be in global memory
+    if (tid == 0) {
+      const int nwait = fz.comb_wait[t];
+      for (int j = 0; j < nwait; ++j)
+        if (!ptx::wait_counter(fz.flags + 8 + j, fz.done_target, abort_word, kWhoAdder)) break;
+      ptx::fence_proxy_async_all();  // they were written by TMA stores
+    }
+    ptx::named_bar_sync(1, kAdderThreads);
+    if (*abort_word != 0) break;
+#ifdef B200S_FUSED_TRACE
+    if (tracer && tid == 0) fz.flags[80 + t] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
+#endif
+    adder_combine<INNER, ALGO, T>(fz.comb, fz.comb_quad[t], first, stride);
+#ifdef B200S_FUSED_TRACE
+    if (tracer && tid == 0) fz.flags[88 + t] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
+#endif
+  }
+}
 
 __device__ __forceinline__ void decode_tile(const GemmKernelParams& p, int tile, int& b, int& mt,
                                             int& nt) {
@@ -128,10 +267,20 @@ __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], 
 //   kNH == 2: tile N = 512 (CTA pair: 256 x 512), both halves share each A block, which cuts the
 //             shared-memory fill traffic per flop by a quarter; the single accumulator set is
 //             drained by 8 epilogue warps before the next tile's first MMA.
-template <int kCtaGroup, int kNH, int kStages, bool kTf32>
-__global__ void __launch_bounds__(64 + 128 * kNH, 1)
+//
+// With F::kOn (the fused Strassen kernel, 256 x 512 tiles only) the CTA has four warpgroups: warps
+// 0-3 producer, MMA issuer and two idle warps; warps 4-11 epilogue; warps 12-15 adders, which form
+// operand blocks and recombine finished quadrants of C (run_adders) beside the products. The
+// producer waits for a group's operand blocks before its first tile of that group, the epilogue
+// warps count every stored tile so that the adders know when a group's products are complete.
+// Registers move from the first warpgroup to the epilogue warpgroups (setmaxnreg).
+template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
+__global__ void __launch_bounds__(F::kOn ? 512 : 64 + 128 * kNH, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const GemmKernelParams p) {
+            const __grid_constant__ CUtensorMap tmC, const GemmKernelParams p,
+            const __grid_constant__ typename F::Params fz) {
+  static_assert(!F::kOn || (kCtaGroup == 2 && kNH == 2 && !kTf32), "the fused kernel exists for 256 x 512 tiles of 16-bit operands");
+  constexpr int kEpiWarp0 = F::kOn ? 4 : 2;      // first epilogue warp
   constexpr int ES = kTf32 ? 4 : 2;              // operand element size
   constexpr int BKE = kRowBytes / ES;            // K elements per stage
   constexpr int BNH = 256;                       // columns of one accumulator half (one tcgen05.mma N)
@@ -200,14 +349,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Fused kernel: 512 threads start with 128 registers each and re-divide them by warpgroup,
+  // 40 (producer, MMA issuer) + 168 + 168 (epilogue) + 136 (adders) per thread.
+  if (warp < kEpiWarp0) {
+  if constexpr (F::kOn) ptx::setmaxnreg_dec<40>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
+      const uint64_t policy_a = ptx::make_l2_policy(p.l2_a), policy_b = ptx::make_l2_policy(p.l2_b);
+      [[maybe_unused]] int group_ready = 0;
+      if constexpr (F::kOn) group_ready = fz.groups_formed;
+#ifdef B200S_FUSED_TRACE
+      const uint64_t trace_p0 = ptx::global_timer_ns();
+#endif
       for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters) {
         int b, mt, nt;
         decode_tile(p, tile, b, mt, nt);
+        if constexpr (F::kOn) {
+          // first tile of a new outer group: every CTA's adders must have stored its operand blocks
+          const int g = b / fz.np2;
+          if (g >= group_ready) {
+#ifdef B200S_FUSED_TRACE
+            const uint64_t w0 = ptx::global_timer_ns();
+#endif
+            if (!ptx::wait_counter(fz.flags + g, fz.ready_target * gridDim.x, abort_word, kWhoProducerGroup)) {
+              alive = false;
+              break;
+            }
+#ifdef B200S_FUSED_TRACE
+            if (blockIdx.x == 0) {
+              fz.flags[32 + g] = static_cast<uint32_t>((ptx::global_timer_ns() - w0) / 1000);       // stall, us
+              fz.flags[40 + g] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_p0) / 1000); // group start, us
+            }
+#endif
+            ptx::fence_proxy_async_all();
+            group_ready = g + 1;
+          }
+        }
         const int m0 = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM;
         const int n0 = nt * BN_TILE + static_cast<int>(cta_rank) * BNH_CTA;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -223,10 +403,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if constexpr (kCtaGroup == 2) fb = ptx::mapa_cluster(fb, 0);
           if (cta_rank == 0) ptx::mbar_expect_tx(full_bar(stage), kCtaGroup * STAGE_BYTES);
           auto load = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
+            const uint64_t policy = m == &tmA ? policy_a : policy_b;
             if constexpr (kCtaGroup == 2)
-              ptx::tma_load_3d_pair(dst, m, fb, c0, c1, b);
+              ptx::tma_load_3d_pair_hint(dst, m, fb, c0, c1, b, policy);
             else
-              ptx::tma_load_3d(dst, m, fb, c0, c1, b);
+              ptx::tma_load_3d_hint(dst, m, fb, c0, c1, b, policy);
           };
           if (!p.a_mn) {
             load(sA, &tmA, k0, m0);
@@ -251,6 +432,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
+#ifdef B200S_FUSED_TRACE
+      if constexpr (F::kOn)
+        if (blockIdx.x == 0) fz.flags[48] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_p0) / 1000);
+#endif
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -309,9 +494,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-  } else {
+  }
+  } else if (warp < kEpiWarp0 + EPI_WARPS) {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 2;          // epilogue warp index
+    if constexpr (F::kOn) ptx::setmaxnreg_inc<168>();
+    const int ew = warp - kEpiWarp0;  // epilogue warp index
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
     const int half = ew >> 2;         // which 256-column half of the tile this warp drains
     const int out_dt = p.out_dtype;
@@ -404,6 +591,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int j = 0; j < 32; ++j) h[j] = hp[g * 32 + j];
           stage_and_store(h, g * 64);
         }
+        if constexpr (F::kOn) {
+          // count this warp's part of the tile once its stores have reached global memory
+          if (lane == 0) {
+            ptx::tma_store_wait_all<0>();
+            ptx::fence_proxy_async_all();
+            __threadfence();
+            ptx::red_release_gpu_add(fz.flags + 8 + b / fz.np2, 1u);
+          }
+          __syncwarp();
+        }
       } else if (p.tma_store) {
 #pragma unroll 1
         for (int gc = 0; gc < BNH; gc += 32) {
@@ -436,6 +633,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     if (p.tma_store && lane == 0) ptx::tma_store_wait_all<0>();  // shared memory must outlive the stores
     __syncwarp();
+  } else {
+    // ------------------------------------------------------------ adders (fused kernel only)
+    if constexpr (F::kOn) {
+      ptx::setmaxnreg_inc<136>();
+      run_adders<F>(fz, abort_word, static_cast<int>(threadIdx.x) - 32 * (kEpiWarp0 + EPI_WARPS));
+    }
   }
 
   // ------------------------------------------------------------ teardown
@@ -505,25 +708,21 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows,
   return B200S_OK;
 }
 
-// m-tiles per raster group: 8 unless B200S_RASTER_GROUP overrides it (tuning experiments).
-int raster_group_setting() {
-  static int value = [] {
-    const char* e = std::getenv("B200S_RASTER_GROUP");
-    int v = e ? std::atoi(e) : 8;
-    return v >= 1 && v <= 64 ? v : 8;
-  }();
-  return value;
-}
+// m-tiles that share a band of n-tiles in the tile order (L2 reuse of the B tiles of a band).
+#ifndef B200S_RASTER_GROUP
+#define B200S_RASTER_GROUP 8
+#endif
+constexpr int kRasterGroup = B200S_RASTER_GROUP;
 
-template <int kCtaGroup, int kNH, int kStages, bool kTf32>
+template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmKernelParams kp,
-                   int sms, cudaStream_t stream) {
-  constexpr int kThreadsV = 64 + 128 * kNH;
+                   const typename F::Params& fz, int sms, cudaStream_t stream) {
+  constexpr int kThreadsV = F::kOn ? 512 : 64 + 128 * kNH;
   constexpr int STAGE_BYTES = kBM * kRowBytes + kNH * (256 / kCtaGroup) * kRowBytes;
   constexpr int STAGING_BYTES = 4 * kNH * (kNH == 1 ? 2 : 1) * 4096;
   constexpr int SMEM = kStages * STAGE_BYTES + STAGING_BYTES + 8 * (2 * kStages + 4) + 16 + 1024;
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
-  auto kernel = gemm_kernel<kCtaGroup, kNH, kStages, kTf32>;
+  auto kernel = gemm_kernel<kCtaGroup, kNH, kStages, kTf32, F>;
 
   // Per-device one-time setup: opt in to the shared-memory size and find out how many
   // clusters can be resident at once (static tile striding needs all of them co-resident).
@@ -559,6 +758,7 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     }
     resident = max_clusters[dev];
   }
+  if (sms / kCtaGroup < resident) resident = sms / kCtaGroup;
 
   const int clusters = kp.total_tiles < resident ? kp.total_tiles : resident;
   cudaLaunchConfig_t cfg = {};
@@ -573,14 +773,21 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  B200S_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, kp));
+  B200S_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmC, kp, fz));
   count_launch();
   return B200S_OK;
 }
 
-}  // namespace
+struct Prepared {
+  CUtensorMap tmA, tmB, tmC;
+  GemmKernelParams kp;
+  int variant, sms;
+  bool tf32;
+};
 
-int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
+// Validates the product, picks the tile variant (forced_variant > 0 overrides), builds the tensor
+// maps and the kernel parameters.
+int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.batch <= 0) return B200S_ERR_BAD_SHAPE;
   if (g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return B200S_ERR_BAD_SHAPE;
   const bool tf32 = g.in_dtype == B200S_FP32;
@@ -597,41 +804,39 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
 
   // Tile variant: 1 = one CTA, 128 x 256 tiles; 2 = CTA pair, 256 x 256 tiles, double-buffered
   // accumulators; 3 = CTA pair, 256 x 512 tiles. Wide outputs default to 3, narrow ones to 2.
-  int variant = g.cta_group;
+  int variant = forced_variant > 0 ? forced_variant : g.cta_group;
   if (variant == 0) variant = (g.N >= 1024 && g.M >= 256) ? 3 : 2;
   const int cta_group = variant == 1 ? 1 : 2;
   const int nh = variant == 3 ? 2 : 1;
   const int BN = 256 * nh;
   const int bke = kRowBytes / static_cast<int>(es);
 
-  CUtensorMap tmA, tmB;
   int rc;
   // K-major operands are stored [rows = M or N][cols = K]; MN-major ones [rows = K][cols = M or N].
   if (g.a_major == B200S_K_MAJOR)
-    rc = make_operand_map(&tmA, g.A, g.in_dtype, g.M, g.K, g.lda, g.batch, g.strideA, kBM);
+    rc = make_operand_map(&out->tmA, g.A, g.in_dtype, g.M, g.K, g.lda, g.batch, g.strideA, kBM);
   else
-    rc = make_operand_map(&tmA, g.A, g.in_dtype, g.K, g.M, g.lda, g.batch, g.strideA, bke);
+    rc = make_operand_map(&out->tmA, g.A, g.in_dtype, g.K, g.M, g.lda, g.batch, g.strideA, bke);
   if (rc) return rc;
   const int bn_cta = 256 / cta_group;  // rows of one B half this CTA loads
   if (g.b_major == B200S_K_MAJOR)
-    rc = make_operand_map(&tmB, g.B, g.in_dtype, g.N, g.K, g.ldb, g.batch, g.strideB, bn_cta);
+    rc = make_operand_map(&out->tmB, g.B, g.in_dtype, g.N, g.K, g.ldb, g.batch, g.strideB, bn_cta);
   else
-    rc = make_operand_map(&tmB, g.B, g.in_dtype, g.K, g.N, g.ldb, g.batch, g.strideB, bke);
+    rc = make_operand_map(&out->tmB, g.B, g.in_dtype, g.K, g.N, g.ldb, g.batch, g.strideB, bke);
   if (rc) return rc;
 
   // The epilogue stores through TMA when C can be described by a tensor map and is overwritten.
   const size_t oes = dtype_size(g.out_dtype);
   const bool tma_store = g.beta == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc * oes) % 16 == 0 &&
                          (g.batch == 1 || (g.strideC * oes) % 16 == 0);
-  CUtensorMap tmC;
   if (tma_store) {
-    rc = make_operand_map(&tmC, g.C, g.out_dtype, g.M, g.N, g.ldc, g.batch, g.strideC, 32, true);
+    rc = make_operand_map(&out->tmC, g.C, g.out_dtype, g.M, g.N, g.ldc, g.batch, g.strideC, 32, true);
     if (rc) return rc;
   } else {
-    tmC = tmA;  // never dereferenced
+    out->tmC = out->tmA;  // never dereferenced
   }
 
-  GemmKernelParams kp;
+  GemmKernelParams& kp = out->kp;
   kp.tma_store = tma_store ? 1 : 0;
   kp.M = static_cast<int32_t>(g.M);
   kp.N = static_cast<int32_t>(g.N);
@@ -642,7 +847,19 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles * g.batch;
   if (total > INT32_MAX) return B200S_ERR_BAD_SHAPE;
   kp.total_tiles = static_cast<int32_t>(total);
-  kp.raster_group = raster_group_setting();
+  kp.raster_group = kRasterGroup;
+  // A grouped launch walks one product after the other, m-band by m-band: the B block of the current
+  // product is read again by every band (and by the next wave of tiles), its A rows only while their
+  // band runs. When a B block fits in L2 with room to spare it is asked to stay (evict last) and the
+  // A rows to leave first; a single large product keeps the default policy.
+  const double b_block_bytes = static_cast<double>(g.N) * static_cast<double>(g.K) * static_cast<double>(es);
+#ifdef B200S_NO_L2_HINTS
+  const bool keep_b = false;
+#else
+  const bool keep_b = g.batch > 1 && b_block_bytes <= 48.0 * 1024 * 1024;
+#endif
+  kp.l2_a = keep_b ? 1 : 0;
+  kp.l2_b = keep_b ? 2 : 0;
   kp.a_mn = g.a_major == B200S_MN_MAJOR;
   kp.b_mn = g.b_major == B200S_MN_MAJOR;
   kp.fmt = tf32 ? 2 : (g.in_dtype == B200S_BF16 ? 1 : 0);
@@ -652,17 +869,128 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   kp.strideC = g.strideC;
   kp.C = g.C;
   kp.status = status;
+  out->variant = variant;
+  out->sms = sms;
+  out->tf32 = tf32;
+  return B200S_OK;
+}
 
-  if (variant == 3) {
-    if (tf32) return launch_variant<2, 2, 4, true>(tmA, tmB, tmC, kp, sms, stream);
-    return launch_variant<2, 2, 4, false>(tmA, tmB, tmC, kp, sms, stream);
+template <int INNER, int ALGO>
+int launch_fused_dtype(const Prepared& pr, const FusedKernelParams& fz, int dtype, cudaStream_t stream) {
+  if (dtype == B200S_BF16)
+    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __nv_bfloat16>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, stream);
+  if (dtype == B200S_FP16)
+    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __half>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, stream);
+  return B200S_ERR_BAD_DTYPE;
+}
+
+}  // namespace
+
+int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
+  Prepared pr;
+  int rc = prepare_gemm(g, 0, &pr);
+  if (rc) return rc;
+  const NoFuse::Params none{};
+  if (pr.variant == 3) {
+    if (pr.tf32) return launch_variant<2, 2, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+    return launch_variant<2, 2, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
   }
-  if (variant == 2) {
-    if (tf32) return launch_variant<2, 1, 6, true>(tmA, tmB, tmC, kp, sms, stream);
-    return launch_variant<2, 1, 6, false>(tmA, tmB, tmC, kp, sms, stream);
+  if (pr.variant == 2) {
+    if (pr.tf32) return launch_variant<2, 1, 6, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+    return launch_variant<2, 1, 6, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
   }
-  if (tf32) return launch_variant<1, 1, 4, true>(tmA, tmB, tmC, kp, sms, stream);
-  return launch_variant<1, 1, 4, false>(tmA, tmB, tmC, kp, sms, stream);
+  if (pr.tf32) return launch_variant<1, 1, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+  return launch_variant<1, 1, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+}
+
+int launch_fused(const FusedArgs& f, cudaStream_t stream) {
+  const GemmArgs& g = f.gemm;
+  const bool wino = f.algo == B200S_ALGO_WINOGRAD;
+  if (!wino && f.algo != B200S_ALGO_CLASSIC) return B200S_ERR_BAD_ALGO;
+  if (f.depth != 1 && f.depth != 2) return B200S_ERR_BAD_DEPTH;
+  if (g.in_dtype != B200S_BF16 && g.in_dtype != B200S_FP16) return B200S_ERR_BAD_DTYPE;
+  if (g.out_dtype != g.in_dtype || g.beta != 0) return B200S_ERR_BAD_DTYPE;  // products are stored in the operand dtype
+  if (!f.flags || !f.A || !f.B || !f.C) return B200S_ERR_NULL_POINTER;
+  if (f.groups_formed < 1 || f.groups_formed > 7) return B200S_ERR_BAD_SHAPE;
+  const int np2 = f.depth == 2 ? 7 : 1;
+  if (g.batch != 7 * np2) return B200S_ERR_BAD_SHAPE;
+  const int sa = wino ? sched::kWinograd : sched::kClassic;
+
+  Prepared pr;
+  int rc = prepare_gemm(g, 3, &pr);
+  if (rc) return rc;
+  if (!pr.kp.tma_store) return B200S_ERR_BAD_ALIGNMENT;
+
+  const size_t es = dtype_size(g.in_dtype);
+  const int vec = static_cast<int>(16 / es);
+  if (f.a_cols_blk % vec || f.b_cols_blk % vec || f.Nb % vec) return B200S_ERR_BAD_SHAPE;
+  if ((f.lda * es) % 16 || (f.ldb * es) % 16) return B200S_ERR_BAD_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(f.A) & 15u) || (reinterpret_cast<uintptr_t>(f.B) & 15u))
+    return B200S_ERR_BAD_ALIGNMENT;
+
+  FusedKernelParams fz = {};
+  int pos[7];
+  for (int i = 0; i < 7; ++i) pos[f.order[i]] = i;
+  for (int side = 0; side < 2; ++side) {
+    pre::PreaddOuterParams& pp = fz.pre[side];
+    pp.X = side == 0 ? f.A : f.B;
+    pp.out = const_cast<void*>(side == 0 ? g.A : g.B);
+    pp.rows_blk = side == 0 ? f.a_rows_blk : f.b_rows_blk;
+    pp.cols_vec = (side == 0 ? f.a_cols_blk : f.b_cols_blk) / vec;
+    pp.ld = side == 0 ? f.lda : f.ldb;
+    pp.strideX = 0;
+    pp.out_batch_blocks = 7 * np2;
+    pp.transposed = side == 0 ? f.a_transposed : f.b_transposed;
+    for (int i = 0; i < 7; ++i) {
+      pre::set_outer_terms(pp, i, sa, side, f.order[i]);
+      pp.out_block0[i] = i * np2;
+    }
+  }
+  comb::CombineOuterParams& cp = fz.comb;
+  cp.products = g.C;
+  cp.C = f.C;
+  cp.Mb = f.Mb;
+  cp.nb_vec = f.Nb / vec;
+  cp.ldc = f.ldc;
+  cp.strideC = 0;
+  cp.batch_blocks = 7 * np2;
+  cp.out_dtype = f.out_dtype;
+  cp.beta = f.beta;
+  const size_t oes = dtype_size(f.out_dtype);
+  cp.vec_ok = ((reinterpret_cast<uintptr_t>(f.C) & 15u) == 0) && ((f.ldc * oes) % 16 == 0) && ((f.Nb * oes) % 16 == 0);
+  for (int e = 0; e < 4; ++e) {
+    cp.quad[e] = static_cast<int8_t>(e);
+    for (int p1 = 0; p1 < 7; ++p1) cp.coef[e][p1] = static_cast<int8_t>(sched::w1(sa, e, p1));
+  }
+  for (int p1 = 0; p1 < 7; ++p1) cp.group_block0[p1] = pos[p1] * np2;
+
+  fz.flags = f.flags;
+  fz.np2 = np2;
+  fz.groups_formed = f.groups_formed;
+  fz.b_formed = f.b_formed ? 1 : 0;
+  fz.ready_target = f.b_formed ? 1u : 2u;  // adder teams per CTA (times the CTAs, in the kernel)
+  fz.done_target = static_cast<uint32_t>(np2) * pr.kp.m_tiles * pr.kp.n_tiles * 2u * 8u;  // 2 CTAs x 8 epilogue warps per tile
+  // The quadrants of C in the order in which the groups feeding them complete.
+  int n = 0;
+  for (int last = 0; last < 7; ++last) {
+    for (int r = 0; r < 4; ++r) {
+      if (!(f.quads_inside & (1 << r))) continue;
+      int lp = 0;
+      for (int p1 = 0; p1 < 7; ++p1)
+        if (sched::w1(sa, r, p1) != 0 && pos[p1] > lp) lp = pos[p1];
+      if (lp != last) continue;
+      fz.comb_quad[n] = static_cast<int8_t>(r);
+      fz.comb_wait[n] = static_cast<int8_t>(lp + 1);
+      ++n;
+    }
+  }
+  fz.n_comb = n;
+
+  if (f.depth == 2)
+    return wino ? launch_fused_dtype<1, sched::kWinograd>(pr, fz, g.in_dtype, stream)
+                : launch_fused_dtype<1, sched::kClassic>(pr, fz, g.in_dtype, stream);
+  return wino ? launch_fused_dtype<0, sched::kWinograd>(pr, fz, g.in_dtype, stream)
+              : launch_fused_dtype<0, sched::kClassic>(pr, fz, g.in_dtype, stream);
 }
 
 }  // namespace b200s

@@ -98,18 +98,79 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity. Returns false (and sets *abort_word,
-// a word in shared memory that all roles of the CTA poll) when the limit runs out
+// a word in shared memory that all roles of the CTA poll) when `limit_ns` of wall clock run out
 // or when another role has already given up.
 // kBackoffNs > 0 sleeps that long between polls: for waits that normally last a whole main loop.
 template <bool kClusterScope = false, int kBackoffNs = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_word, uint32_t who) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile uint32_t* abort_word,
+                                                uint32_t who, uint64_t limit_ns) {
   uint64_t start = 0;
   for (uint32_t it = 0;; ++it) {
     bool ok = kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
     if (ok) return true;
     if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
-    if ((it & 0xffu) == 0xffu) {
+    if ((it & 0xfu) == 0xfu) {
+      if (*abort_word != 0) return false;
+      uint64_t now = global_timer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > limit_ns) {
+        *abort_word = who;
+        return false;
+      }
+    }
+  }
+}
+template <bool kClusterScope = false, int kBackoffNs = 0>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_word, uint32_t who) {
+  return mbar_wait_limit<kClusterScope, kBackoffNs>(bar, parity, abort_word, who, kWaitLimitNs);
+}
+
+// ---- register reallocation between warpgroups --------------------------------------------------
+// All four warps of a warpgroup execute these together. A kernel launched with R registers per
+// thread may hand registers of its light warpgroups (dec) to its heavy ones (inc); the sum over the
+// warpgroups must stay within the register file.
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// Barrier `id` (1..15) among `nthreads` threads of the CTA (whole warps).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Orders this thread's generic-proxy accesses with async-proxy accesses (TMA) to the same memory, in
+// both directions: before publishing data that a TMA load elsewhere will read, and before reading
+// with ordinary loads what a completed TMA store wrote.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// ---- counters in global memory shared by the CTAs of one launch ---------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* ptr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// Publishes everything this thread (and, through a preceding CTA barrier, its CTA) wrote before it.
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* ptr, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+// Waits until *ctr >= target, with the same wall-clock limit and abort protocol as mbar_wait.
+__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, volatile uint32_t* abort_word,
+                                             uint32_t who) {
+  uint64_t start = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (ld_acquire_gpu(ctr) >= target) return true;
+    __nanosleep(256);
+    if ((it & 0x3fu) == 0x3fu) {
       if (*abort_word != 0) return false;
       uint64_t now = global_timer_ns();
       if (start == 0) {
@@ -168,6 +229,35 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// The same two loads with an L2 cache policy (a word from make_l2_policy) for the fetched lines.
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1,
+                                                 int c2, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                      int c0, int c1, int c2, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
+// L2 cache policy words: 0 = evict normal, 1 = evict first, 2 = evict last.
+__device__ __forceinline__ uint64_t make_l2_policy(int kind) {
+  uint64_t policy;
+  if (kind == 1)
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  else if (kind == 2)
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  else
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
 
 // Tiled 3-D store shared -> global (bulk async group).

@@ -67,7 +67,7 @@ def _operand(t: torch.Tensor):
 
 
 def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precision=None,
-                 tile_variant=0, pipeline=0, b_blocks_ready=False):
+                 tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0):
     """Fill a ``b200s_problem`` for C (+)= A @ B. Returns (problem, A', B') where A'/B' are the
     tensors whose pointers must be passed (copies only when the strides force one)."""
     if A.dim() != B.dim() or A.dim() not in (2, 3):
@@ -104,6 +104,7 @@ def make_problem(A, B, C, algo="auto", depth=-1, beta=0, prod_dtype=None, precis
     p.tile_variant = int(tile_variant)
     p.pipeline = int(pipeline)
     p.b_blocks_ready = 1 if b_blocks_ready else 0
+    p.fuse = int(fuse)
     return p, A2, B2
 
 
@@ -120,12 +121,13 @@ def resolve(p: "_lib.Problem"):
 
 
 def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto", depth=-1, beta=0,
-               prod_dtype=None, precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False,
+               prod_dtype=None, precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0,
                workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B (beta=0) or C += A @ B (beta=1) on the current CUDA stream. Returns C."""
     _require_cuda(A, B, C)
     lib = _lib.load()
-    p, A2, B2 = make_problem(A, B, C, algo, depth, beta, prod_dtype, precision, tile_variant, pipeline, b_blocks_ready)
+    p, A2, B2 = make_problem(A, B, C, algo, depth, beta, prod_dtype, precision, tile_variant, pipeline, b_blocks_ready,
+                             fuse)
     with torch.cuda.device(C.device):
         need = workspace_bytes(p)
         ws_ptr = None
@@ -143,13 +145,13 @@ def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto"
 
 
 def matmul(A: torch.Tensor, B: torch.Tensor, *, algo="auto", depth=-1, out_dtype=None, prod_dtype=None,
-           precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, workspace=None) -> torch.Tensor:
+           precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0, workspace=None) -> torch.Tensor:
     """A @ B as a new tensor of ``out_dtype`` (default: the operand dtype)."""
     _require_cuda(A, B)
     shape = (A.shape[-2], B.shape[-1]) if A.dim() == 2 else (A.shape[0], A.shape[-2], B.shape[-1])
     C = torch.empty(shape, dtype=out_dtype or A.dtype, device=A.device)
     return matmul_out(A, B, C, algo=algo, depth=depth, beta=0, prod_dtype=prod_dtype, precision=precision,
-                      tile_variant=tile_variant, pipeline=pipeline, b_blocks_ready=b_blocks_ready,
+                      tile_variant=tile_variant, pipeline=pipeline, b_blocks_ready=b_blocks_ready, fuse=fuse,
                       workspace=workspace)
 
 

@@ -56,19 +56,22 @@ def ws_bytes(lib, p):
     return rc, n.value
 
 
+FLAGS = 256   # counters of the fused schedule, at the end of every one- or two-level scratch
+
+
 def test_workspace_layout(lib):
     rc, n = ws_bytes(lib, problem())
     blk = 256 * 256 * 2
-    assert rc == 0 and n == 3 * 49 * blk
+    assert rc == 0 and n == 3 * 49 * blk + FLAGS
     rc, n = ws_bytes(lib, problem(depth=1))
-    assert rc == 0 and n == 3 * 7 * 512 * 512 * 2
+    assert rc == 0 and n == 3 * 7 * 512 * 512 * 2 + FLAGS
     rc, n = ws_bytes(lib, problem(depth=1, prod_dtype=_lib.FP32))
-    assert rc == 0 and n == 2 * 7 * 512 * 512 * 2 + 7 * 512 * 512 * 4
+    assert rc == 0 and n == 2 * 7 * 512 * 512 * 2 + 7 * 512 * 512 * 4 + FLAGS
     rc, n = ws_bytes(lib, problem(algo=_lib.ALGO_DENSE))
     assert rc == 0 and n == 0
     # three levels: one outer level (7 blocks of 512^2 per side and 7 products) around a two-level 512^3 product
     rc, n = ws_bytes(lib, problem(depth=3))
-    assert rc == 0 and n == 3 * 7 * 512 * 512 * 2 + 3 * 49 * 128 * 128 * 2
+    assert rc == 0 and n == 3 * 7 * 512 * 512 * 2 + 3 * 49 * 128 * 128 * 2 + FLAGS
 
 
 @pytest.mark.parametrize("kw,status", [
