@@ -156,9 +156,12 @@ int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_dev
  * allocating library routine.
  *
  * Limit: b200s_workspace_bytes(p) must not exceed 64 MiB (for bf16: depth 1 up to about 2048^3,
- * depth 2 up to about 1792^3; any size at depth 0); larger problems return B200S_ERR_TOO_LARGE and
- * launch nothing. Always the sequential schedule on `stream`; `pipeline` and `b_blocks_ready` are
- * ignored, and fp32 operands always run as one TF32 pass.
+ * depth 2 up to about 1792^3; at depth 0 any size of 16-bit operands, while fp32 operands given
+ * MN-major need their K-major copy to fit, i.e. M*K*4 and K*N*4 bytes); larger problems return
+ * B200S_ERR_TOO_LARGE and launch nothing. Always the sequential schedule on `stream`; `pipeline`,
+ * `fuse` and `b_blocks_ready` are ignored. fp32 operands run as one TF32 pass: a problem that asks
+ * for B200S_PREC_3XTF32 is refused with B200S_ERR_BAD_DTYPE rather than silently run at lower
+ * precision.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and the
  * device's properties; make that first call outside any stream capture. All calls share the one
@@ -166,10 +169,12 @@ int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_dev
  * has written first, so nothing needs clearing - but two calls whose kernels can overlap on the GPU
  * (different streams, or several host threads) overwrite each other's blocks and give wrong
  * results. Serialise them on one stream. A wait that gives up inside this call is recorded in
- * status words of the library image, not in those b200s_device_status reads.
+ * status words of the library image, not in those b200s_device_status reads: b200s_static_status
+ * reads (and clears) them the same way, device -> host on `stream`, again without allocating.
  */
 int b200s_matmul_static(const b200s_problem* p, const void* A_device, const void* B_device, void* C_device,
                         void* stream);
+int b200s_static_status(void* stream, int32_t* status_out, int32_t* detail_out);
 
 /*
  * The algorithm and depth b200s_matmul will use for p (resolves AUTO / -1 through the tuner
@@ -198,6 +203,29 @@ int b200s_tuner_lookup(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_
  */
 int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out);
 
+/*
+ * Self-test of the bounded device-side waits: launches a one-thread kernel that waits limit_ns
+ * (1 .. 10^9) on a barrier nobody signals, gives up, and reports it in the status words exactly as
+ * a stalled GEMM role would. Afterwards b200s_device_status returns B200S_ERR_DEVICE_TIMEOUT with
+ * detail 7 once, then B200S_OK again. The kernel owns no TMA transfer and no tensor memory, so
+ * nothing is left in flight when it returns. No counterpart in the reference.
+ */
+int b200s_wait_probe(uint64_t limit_ns, void* stream);
+
+/*
+ * Stage timing of b200s_matmul calls (the per-kernel rows the reference reads from torch.profiler in
+ * its profiling scripts, main_profiling.py:197-229 for the totals). Between _begin and _end every
+ * call that runs the sequential or the fused schedule on the current device records an event on its
+ * stream at each stage boundary, for at most max_calls (1..4096) calls. _end waits for the recorded
+ * calls, writes the mean duration in milliseconds of the four stages to stage_ms_out[0..3] - operand
+ * blocks of A, operand blocks of B, products, recombination; in the fused schedule: blocks of A of the
+ * first group, blocks of B of the first group, the fused kernel, the recombination left after it -
+ * and the number of calls measured to *calls_out. Other schedules (pipelined, more than two levels,
+ * dense) record nothing. One collection at a time, process-wide.
+ */
+int b200s_profile_begin(int max_calls);
+int b200s_profile_end(float* stage_ms_out, int32_t* calls_out);
+
 /* Number of kernels this library has launched in the calling process (for benchmarks' accounting). */
 int64_t b200s_launch_count(void);
 
@@ -222,6 +250,30 @@ int b200s_combine(const b200s_problem* p, const void* products_device, void* C_d
  */
 int b200s_combine_peers(const b200s_problem* p, const void* products_device, void* const* C_list, int n_dst,
                         void* stream);
+
+/*
+ * b200s_matmul whose result goes to n_dst (1..8) destinations at once: C_list[i] is the device address
+ * of element (0,0) of the product inside destination i, all with leading dimension p->ldc; beta must
+ * be 0 and batch 1. A dense product stores every finished tile to all destinations from the GEMM's
+ * TMA-store epilogue (so the exchange of a row-sharded product rides on the product kernel, tile by
+ * tile, and needs C rows that are multiples of 16 bytes); a one- or two-level Strassen product runs its
+ * sequential schedule and ends in b200s_combine_peers. Destinations may be other GPUs' memory mapped
+ * into this process; only stores go there, every load reads this GPU's memory. The reference has no
+ * multi-GPU product: this is the per-rank step of the row-sharded one.
+ */
+int b200s_matmul_peers(const b200s_problem* p, const void* A_device, const void* B_device, void* const* C_list,
+                       int n_dst, void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
+ * Barrier number `epoch` among `world` (1..8) GPUs on `stream`: pads[r] is rank r's pad of at least
+ * `world` 32-bit slots, zero before the first barrier, reachable from this GPU. The kernel stores
+ * `epoch` into slot `rank` of every pad and waits until all slots of pads[rank] have reached it; use
+ * epochs 1, 2, 3, ... The wait is bounded by limit_ns: when it runs out the kernel reports
+ * B200S_ERR_DEVICE_TIMEOUT with detail 8 through b200s_device_status and returns - it does not trap,
+ * so a rank that died between steps costs its peers one limit, not their context. No counterpart in
+ * the reference.
+ */
+int b200s_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, uint64_t limit_ns, void* stream);
 
 /*
  * Copies `bytes` (a multiple of 16, both ends 16-byte aligned) from src_device to n_dst (1..8)

@@ -79,10 +79,18 @@ SIGNATURES = {
     "b200s_tuner_lookup": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
                                           _P(ctypes.c_int32), _P(ctypes.c_int32)]),
     "b200s_device_status": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int32), _P(ctypes.c_int32)]),
+    "b200s_wait_probe": (ctypes.c_int, [ctypes.c_uint64, ctypes.c_void_p]),
+    "b200s_static_status": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int32), _P(ctypes.c_int32)]),
     "b200s_launch_count": (ctypes.c_int64, []),
+    "b200s_profile_begin": (ctypes.c_int, [ctypes.c_int]),
+    "b200s_profile_end": (ctypes.c_int, [_P(ctypes.c_float), _P(ctypes.c_int32)]),
     "b200s_preadd": (ctypes.c_int, [_P(Problem), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "b200s_combine_peers": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int,
                                            ctypes.c_void_p]),
+    "b200s_matmul_peers": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int,
+                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "b200s_peer_barrier": (ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_uint32,
+                                          ctypes.c_uint64, ctypes.c_void_p]),
     "b200s_push_rows": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,
                                        ctypes.c_void_p]),
     "b200s_combine": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),

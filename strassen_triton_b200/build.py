@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libb200s.so")
-SOURCES = ["api.cu", "gemm_sm100.cu", "preadd.cu", "combine.cu", "transpose.cu"]
+SOURCES = ["api.cu", "gemm_sm100.cu", "preadd.cu", "combine.cu", "transpose.cu", "peer.cu"]
 
 
 def _nvcc() -> str:

@@ -23,6 +23,27 @@ namespace {
 thread_local char g_cuda_error[512] = "";
 std::atomic<int64_t> g_launches{0};
 
+// ---- stage timing (b200s_profile_begin / _end) ----------------------------------------------
+// While collection is on, the sequential and the fused schedule of b200s_matmul record an event on
+// the caller's stream at every stage boundary: start, after the operand blocks of A, after those of
+// B, after the products (the fused kernel, in the fused schedule), after the recombination.
+constexpr int kProfMarks = 5;
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+int g_prof_max = 0, g_prof_calls = 0;
+std::vector<cudaEvent_t> g_prof_ev;
+
+// Returns the slot of a new call (or -1 when collection is off or full).
+int prof_new_call() {
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  if (!g_prof_on || g_prof_calls >= g_prof_max) return -1;
+  return g_prof_calls++;
+}
+void prof_mark(int slot, int k, cudaStream_t stream) {
+  if (slot < 0) return;
+  cudaEventRecord(g_prof_ev[static_cast<size_t>(slot) * kProfMarks + k], stream);
+}
+
 struct DeviceState {
   bool ready = false;
   bool ok = false;
@@ -369,6 +390,8 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
   int pos[7];
   for (int i = 0; i < 7; ++i) pos[order[i]] = i;
   const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
+  const int prof = prof_new_call();
+  prof_mark(prof, 0, stream);
 
 #ifdef B200S_FUSED_TRACE
   // development build: the kernel leaves timestamps of CTA 0 behind the counters (the scratch is
@@ -392,6 +415,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
   pa.ld = p->lda, pa.transposed = !a_k;
   int rc = launch_preadd_outer(pa, stream);
   if (rc) return rc;
+  prof_mark(prof, 1, stream);
   PreaddOuterArgs pb = pa;
   pb.X = B, pb.out = Sb, pb.side = 1;
   pb.rows_blk = b_k ? plan.Nb : plan.Kb, pb.cols_blk = b_k ? plan.Kb : plan.Nb;
@@ -400,6 +424,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
     rc = launch_preadd_outer(pb, stream);
     if (rc) return rc;
   }
+  prof_mark(prof, 2, stream);
   int formed = 1;
   if (dbg & 1) {
     // every group formed before the kernel
@@ -443,6 +468,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
   f.flags = flags;
   rc = launch_fused(f, stream);
   if (rc) return rc;
+  prof_mark(prof, 3, stream);
 
   if (tail_mask) {
     CombineOuterArgs ca;
@@ -457,6 +483,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
     rc = launch_combine_outer(ca, stream);
     if (rc) return rc;
   }
+  prof_mark(prof, 4, stream);
   return B200S_OK;
 }
 
@@ -650,9 +677,10 @@ int b200s_push_rows(const void* src, void* const* dst_list, int n_dst, size_t by
   return launch_push_rows(src, dst_list, n_dst, bytes, static_cast<cudaStream_t>(stream));
 }
 
-int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* workspace,
-                 size_t workspace_bytes, void* stream_v) {
-  if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;
+// C (+)= A . B into C, or (n_dst > 0, beta 0, one product) into every destination of dst_list.
+static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* const* dst_list,
+                      int n_dst, void* workspace, size_t workspace_bytes, void* stream_v) {
+  if (!p_in || !A || !B || (!C && n_dst == 0)) return B200S_ERR_NULL_POINTER;
   Plan plan;
   int rc = make_plan(p_in, &plan);
   if (rc) return rc;
@@ -687,7 +715,10 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
     p->b_major = B200S_K_MAJOR, p->ldb = p->K, p->strideB = p->K * p->N;
   }
 
-  if (plan.depth > 2) return run_deep(p, plan, A, B, C, ws + plan.ta_bytes + plan.tb_bytes, stream);
+  if (plan.depth > 2) {
+    if (n_dst > 0) return B200S_ERR_BAD_DEPTH;  // several destinations: dense, or one pipeline of up to two levels
+    return run_deep(p, plan, A, B, C, ws + plan.ta_bytes + plan.tb_bytes, stream);
+  }
 
   GemmArgs g;
   g.cta_group = p->tile_variant;
@@ -699,6 +730,7 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   uint8_t* B3 = A3 + plan.a3_bytes;
   if (plan.depth == 0) {
     g.A = A, g.B = B, g.C = C;
+    g.n_dst = n_dst, g.C_list = dst_list;
     g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
     g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
     g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
@@ -724,7 +756,8 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
   // The fused schedule: asked for (fuse 1 / 3), or the library's choice (fuse 0) for products from
   // kFusedFrom^3 on when the caller left the schedule open.
-  if (p->fuse == 1 || p->fuse == 3 || (p->fuse == 0 && p->pipeline == 0 && volume >= kFusedFrom * kFusedFrom * kFusedFrom)) {
+  if (n_dst == 0 &&
+      (p->fuse == 1 || p->fuse == 3 || (p->fuse == 0 && p->pipeline == 0 && volume >= kFusedFrom * kFusedFrom * kFusedFrom))) {
     if (fused_eligible(p, plan)) {
       uint32_t* flags = reinterpret_cast<uint32_t*>(ws + plan.total_bytes - plan.flag_bytes);
       return run_fused(p, plan, A, B, C, Sa, Sb, Mp, flags, p->fuse == 3, stream);
@@ -733,14 +766,18 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   }
   // Large single products run the pipelined driver unless the caller chose otherwise.
   const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 24576.0 * 24576.0 * 24576.0);
-  if (p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
+  if (n_dst == 0 && p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 
+  const int prof = prof_new_call();
+  prof_mark(prof, 0, stream);
   rc = b200s_preadd(p, 0, A, Sa, stream_v);
   if (rc) return rc;
+  prof_mark(prof, 1, stream);
   if (!p->b_blocks_ready) {
     rc = b200s_preadd(p, 1, B, Sb, stream_v);
     if (rc) return rc;
   }
+  prof_mark(prof, 2, stream);
 
   const bool a_k = p->a_major == B200S_K_MAJOR, b_k = p->b_major == B200S_K_MAJOR;
   g.A = Sa, g.B = Sb, g.C = Mp;
@@ -769,8 +806,30 @@ int b200s_matmul(const b200s_problem* p_in, const void* A, const void* B, void* 
   }
   rc = launch_gemm(g, stream);
   if (rc) return rc;
+  prof_mark(prof, 3, stream);
 
-  return b200s_combine(p, Mp, C, stream_v);
+  rc = n_dst > 0 ? b200s_combine_peers(p, Mp, dst_list, n_dst, stream_v) : b200s_combine(p, Mp, C, stream_v);
+  prof_mark(prof, 4, stream);
+  return rc;
+}
+
+int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+  if (!C) return B200S_ERR_NULL_POINTER;
+  return run_matmul(p, A, B, C, nullptr, 0, workspace, workspace_bytes, stream);
+}
+
+int b200s_matmul_peers(const b200s_problem* p, const void* A, const void* B, void* const* C_list, int n_dst,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p || !C_list) return B200S_ERR_NULL_POINTER;
+  if (n_dst < 1 || n_dst > 8 || p->batch != 1 || p->beta != 0) return B200S_ERR_BAD_SHAPE;
+  for (int d = 0; d < n_dst; ++d)
+    if (!C_list[d]) return B200S_ERR_NULL_POINTER;
+  return run_matmul(p, A, B, nullptr, C_list, n_dst, workspace, workspace_bytes, stream);
+}
+
+int b200s_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, uint64_t limit_ns, void* stream) {
+  return launch_peer_barrier(pads, rank, world, epoch, limit_ns, static_cast<cudaStream_t>(stream));
 }
 
 // ---- product with built-in scratch ---------------------------------------------------------------
@@ -822,9 +881,8 @@ int static_state(StaticState** out) {
 
 int b200s_matmul_static(const b200s_problem* p_in, const void* A, const void* B, void* C, void* stream_v) {
   if (!p_in || !A || !B || !C) return B200S_ERR_NULL_POINTER;
-  b200s_problem single_pass = *p_in;
-  single_pass.precision = B200S_PREC_TF32;  // this entry runs fp32 operands as one TF32 pass
-  p_in = &single_pass;
+  // fp32 operands run as one TF32 pass here; the three-pass mode needs more scratch than this entry has
+  if (p_in->in_dtype == B200S_FP32 && p_in->precision == B200S_PREC_3XTF32) return B200S_ERR_BAD_DTYPE;
   Plan plan;
   int rc = make_plan(p_in, &plan);
   if (rc) return rc;
@@ -902,6 +960,30 @@ int b200s_matmul_static(const b200s_problem* p_in, const void* A, const void* B,
   return launch_combine(c, stream);
 }
 
+int b200s_wait_probe(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return B200S_ERR_BAD_SHAPE;  // at most one second
+  if (!device_status_words()) return B200S_ERR_NO_DEVICE;
+  return launch_wait_probe(limit_ns, static_cast<cudaStream_t>(stream));
+}
+
+int b200s_static_status(void* stream, int32_t* status_out, int32_t* detail_out) {
+  if (!status_out) return B200S_ERR_NULL_POINTER;
+  StaticState* st = nullptr;
+  int rc = static_state(&st);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t host[2] = {0, 0};
+  B200S_CUDA_OK(cudaMemcpyAsync(host, st->status, sizeof(host), cudaMemcpyDeviceToHost, s));
+  B200S_CUDA_OK(cudaStreamSynchronize(s));
+  if (host[0] != 0) {
+    B200S_CUDA_OK(cudaMemsetAsync(st->status, 0, sizeof(host), s));
+    B200S_CUDA_OK(cudaStreamSynchronize(s));
+  }
+  *status_out = host[0] ? B200S_ERR_DEVICE_TIMEOUT : B200S_OK;
+  if (detail_out) *detail_out = static_cast<int32_t>(host[1]);
+  return B200S_OK;
+}
+
 int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out) {
   if (!status_out) return B200S_ERR_NULL_POINTER;
   uint32_t* words = device_status_words();
@@ -917,6 +999,42 @@ int b200s_device_status(void* stream, int32_t* status_out, int32_t* detail_out) 
   *status_out = host[0] ? B200S_ERR_DEVICE_TIMEOUT : B200S_OK;
   if (detail_out) *detail_out = static_cast<int32_t>(host[1]);
   return B200S_OK;
+}
+
+// ---- stage timing ------------------------------------------------------------------------------
+
+int b200s_profile_begin(int max_calls) {
+  if (max_calls < 1 || max_calls > 4096) return B200S_ERR_BAD_SHAPE;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  for (cudaEvent_t e : g_prof_ev) cudaEventDestroy(e);
+  g_prof_ev.assign(static_cast<size_t>(max_calls) * kProfMarks, nullptr);
+  for (auto& e : g_prof_ev) B200S_CUDA_OK(cudaEventCreate(&e));
+  g_prof_max = max_calls, g_prof_calls = 0, g_prof_on = true;
+  return B200S_OK;
+}
+
+int b200s_profile_end(float* stage_ms_out, int32_t* calls_out) {
+  if (!stage_ms_out || !calls_out) return B200S_ERR_NULL_POINTER;
+  std::lock_guard<std::mutex> lock(g_prof_mu);
+  g_prof_on = false;
+  for (int k = 0; k + 1 < kProfMarks; ++k) stage_ms_out[k] = 0.f;
+  *calls_out = g_prof_calls;
+  int rc = B200S_OK;
+  for (int c = 0; c < g_prof_calls && rc == B200S_OK; ++c) {
+    cudaEvent_t* ev = &g_prof_ev[static_cast<size_t>(c) * kProfMarks];
+    if (cudaEventSynchronize(ev[kProfMarks - 1]) != cudaSuccess) rc = B200S_ERR_CUDA;
+    for (int k = 0; k + 1 < kProfMarks && rc == B200S_OK; ++k) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, ev[k], ev[k + 1]) != cudaSuccess) rc = B200S_ERR_CUDA;
+      stage_ms_out[k] += ms;
+    }
+  }
+  if (rc == B200S_OK && g_prof_calls > 0)
+    for (int k = 0; k + 1 < kProfMarks; ++k) stage_ms_out[k] /= static_cast<float>(g_prof_calls);
+  for (cudaEvent_t e : g_prof_ev) cudaEventDestroy(e);
+  g_prof_ev.clear();
+  g_prof_max = g_prof_calls = 0;
+  return rc;
 }
 
 // ---- tuner -----------------------------------------------------------------------------------

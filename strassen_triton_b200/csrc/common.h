@@ -45,8 +45,15 @@ struct GemmArgs {
   // state of api.cu (nullptr / 0 = use that state).
   uint32_t* status = nullptr;
   int sms = 0;
+  // Optional: n_dst > 0 stores C to C_list[0 .. n_dst) instead of C (same ldc everywhere; needs the
+  // TMA-store epilogue: beta 0, 16-byte aligned rows). Destinations may be peer GPUs' memory.
+  int n_dst = 0;
+  void* const* C_list = nullptr;
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
+// One-thread kernel that waits `limit_ns` on a barrier nobody signals and reports the give-up in the
+// device status words (the self-test behind b200s_wait_probe).
+int launch_wait_probe(uint64_t limit_ns, cudaStream_t stream);
 
 // ---- fused Strassen kernel (gemm_sm100.cu) ------------------------------------------------
 // One persistent launch that runs the grouped product over all 7^depth operand blocks while four
@@ -104,6 +111,9 @@ struct CombineArgs {
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 // The same recombination written to n_dst (<= 8) copies of C at once (a.C and a.beta are ignored).
 int launch_combine_peers(const CombineArgs& a, void* const* dst, int n_dst, cudaStream_t stream);
+// Barrier number `epoch` among `world` GPUs over pads of 32-bit slots (peer.cu); bounded by limit_ns.
+int launch_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, uint64_t limit_ns,
+                        cudaStream_t stream);
 // Contiguous copy of `bytes` (a multiple of 16) from src to n_dst (<= 8) destinations, small SM footprint.
 int launch_push_rows(const void* src, void* const* dst, int n_dst, size_t bytes, cudaStream_t stream);
 

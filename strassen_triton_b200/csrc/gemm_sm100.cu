@@ -49,6 +49,7 @@ struct GemmKernelParams {
   int32_t out_dtype, beta;
   int32_t tma_store;          // 1: the epilogue stages tiles in shared memory and stores them with TMA
   int32_t l2_a, l2_b;         // L2 policy of the operand loads (ptx::make_l2_policy kinds)
+  int32_t n_dst;              // copies of C the TMA-store epilogue writes (1 unless the product is exchanged)
   int64_t ldc, strideC;
   void* C;
   uint32_t* status;
@@ -61,7 +62,8 @@ enum : uint32_t {
   kWhoMmaAcc = 3,
   kWhoEpilogue = 4,
   kWhoProducerGroup = 5,  // fused kernel: the producer waiting for a group's operand blocks
-  kWhoAdder = 6           // fused kernel: an adder warp waiting for a group's products
+  kWhoAdder = 6,          // fused kernel: an adder warp waiting for a group's products
+  kWhoProbe = 7           // wait_probe_kernel: the self-test of the bounded wait
 };
 
 // ---- fused Strassen kernel: what the adder warps do ----------------------------------------------
@@ -261,6 +263,14 @@ __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], 
   }
 }
 
+// Tensor maps of the destinations of C. A row-sharded product stores every finished tile into each
+// GPU's copy of C (peer memory mapped into this process): the exchange is part of the epilogue, tile
+// by tile, over NVLink. Stores only - every load of this kernel reads this GPU's own memory.
+constexpr int kMaxDst = 8;
+struct CMaps {
+  CUtensorMap m[kMaxDst];
+};
+
 // kNH = number of 256-column accumulator halves one tile owns.
 //   kNH == 1: tile N = 256, two accumulators used alternately, so the epilogue of tile i overlaps
 //             the main loop of tile i+1; 4 epilogue warps.
@@ -277,7 +287,7 @@ __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&r)[32], 
 template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
 __global__ void __launch_bounds__(F::kOn ? 512 : 64 + 128 * kNH, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const GemmKernelParams p,
+            const __grid_constant__ CMaps tmC, const GemmKernelParams p,
             const __grid_constant__ typename F::Params fz) {
   static_assert(!F::kOn || (kCtaGroup == 2 && kNH == 2 && !kTf32), "the fused kernel exists for 256 x 512 tiles of 16-bit operands");
   constexpr int kEpiWarp0 = F::kOn ? 4 : 2;      // first epilogue warp
@@ -334,7 +344,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
-    if (p.tma_store) ptx::prefetch_tensormap(&tmC);
+    if (p.tma_store)
+      for (int d = 0; d < p.n_dst; ++d) ptx::prefetch_tensormap(&tmC.m[d]);
   }
   if (warp == 1) {
     ptx::tmem_alloc<kCtaGroup>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -553,7 +564,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_3d_hint(&tmC, sbuf, col0 + gc, row_warp, b, store_policy);
+          for (int d = 0; d < p.n_dst; ++d)
+            ptx::tma_store_3d_hint(&tmC.m[d], sbuf, col0 + gc, row_warp, b, store_policy);
           ptx::tma_store_commit();
         }
         if constexpr (STG_BUFS == 2) stage_flip ^= 1;
@@ -715,7 +727,7 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows,
 constexpr int kRasterGroup = B200S_RASTER_GROUP;
 
 template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
-int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmKernelParams kp,
+int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, GemmKernelParams kp,
                    const typename F::Params& fz, int sms, cudaStream_t stream) {
   constexpr int kThreadsV = F::kOn ? 512 : 64 + 128 * kNH;
   constexpr int STAGE_BYTES = kBM * kRowBytes + kNH * (256 / kCtaGroup) * kRowBytes;
@@ -779,7 +791,8 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
 }
 
 struct Prepared {
-  CUtensorMap tmA, tmB, tmC;
+  CUtensorMap tmA, tmB;
+  CMaps tmC;
   GemmKernelParams kp;
   int variant, sms;
   bool tf32;
@@ -829,15 +842,24 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   const size_t oes = dtype_size(g.out_dtype);
   const bool tma_store = g.beta == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc * oes) % 16 == 0 &&
                          (g.batch == 1 || (g.strideC * oes) % 16 == 0);
-  if (tma_store) {
-    rc = make_operand_map(&out->tmC, g.C, g.out_dtype, g.M, g.N, g.ldc, g.batch, g.strideC, 32, true);
-    if (rc) return rc;
-  } else {
-    out->tmC = out->tmA;  // never dereferenced
+  const int n_dst = g.n_dst > 0 ? g.n_dst : 1;
+  if (n_dst > kMaxDst) return B200S_ERR_BAD_SHAPE;
+  if (n_dst > 1 && !tma_store) return B200S_ERR_BAD_ALIGNMENT;  // several destinations exist only for the TMA-store epilogue
+  for (int d = 0; d < kMaxDst; ++d) {
+    if (tma_store && d < n_dst) {
+      void* dst = g.n_dst > 0 ? g.C_list[d] : g.C;
+      if (!dst) return B200S_ERR_NULL_POINTER;
+      if (reinterpret_cast<uintptr_t>(dst) & 15u) return B200S_ERR_BAD_ALIGNMENT;
+      rc = make_operand_map(&out->tmC.m[d], dst, g.out_dtype, g.M, g.N, g.ldc, g.batch, g.strideC, 32, true);
+      if (rc) return rc;
+    } else {
+      out->tmC.m[d] = out->tmA;  // never dereferenced
+    }
   }
 
   GemmKernelParams& kp = out->kp;
   kp.tma_store = tma_store ? 1 : 0;
+  kp.n_dst = n_dst;
   kp.M = static_cast<int32_t>(g.M);
   kp.N = static_cast<int32_t>(g.N);
   const int tile_m = kBM * cta_group;
@@ -884,7 +906,36 @@ int launch_fused_dtype(const Prepared& pr, const FusedKernelParams& fz, int dtyp
   return B200S_ERR_BAD_DTYPE;
 }
 
+// ---- self-test of the bounded wait ---------------------------------------------------------------
+// One thread waits on an mbarrier that nobody ever arrives on, with the caller's limit instead of the
+// kernels' two seconds, and reports the give-up exactly as the GEMM roles do: abort word, then the
+// device status words. Nothing else runs in the CTA (no TMA, no tensor memory), so running out of
+// time leaves nothing in flight.
+__global__ void __launch_bounds__(32) wait_probe_kernel(uint64_t limit_ns, uint32_t* status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_mbar_init();
+    const bool ok = ptx::mbar_wait_limit<false, 64>(ptx::smem_u32(&bar), 0u, &abort_word, kWhoProbe, limit_ns);
+    if (!ok) {
+      atomicExch(&status[0], 1u);
+      atomicExch(&status[1], abort_word);
+    }
+  }
+}
+
 }  // namespace
+
+int launch_wait_probe(uint64_t limit_ns, cudaStream_t stream) {
+  uint32_t* status = device_status_words();
+  if (!status) return B200S_ERR_NO_DEVICE;
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, status);
+  B200S_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return B200S_OK;
+}
 
 int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   Prepared pr;

@@ -6,6 +6,7 @@ the CUDA library through its C ABI.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional
 
@@ -163,6 +164,28 @@ def device_status(device=None):
         stream = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.b200s_device_status(stream, ctypes.byref(s), ctypes.byref(d)))
     return s.value, d.value
+
+
+STAGES = ("operand_blocks_A", "operand_blocks_B", "products", "recombination")
+
+
+@contextlib.contextmanager
+def stage_timing(max_calls: int = 256):
+    """Collect the library's per-stage event timing for the matmul calls made inside the block.
+    Yields a dict that, after the block, holds the mean milliseconds of the four stages (keys
+    ``STAGES``; in the fused schedule: the first group's blocks of A and of B, the fused kernel, the
+    recombination left after it) and ``calls``, the number of calls measured."""
+    lib = _lib.load()
+    _lib.check(lib.b200s_profile_begin(int(max_calls)))
+    out = {}
+    try:
+        yield out
+    finally:
+        ms = (ctypes.c_float * 4)()
+        calls = ctypes.c_int32(0)
+        _lib.check(lib.b200s_profile_end(ms, ctypes.byref(calls)))
+        out.update({k: float(ms[i]) for i, k in enumerate(STAGES)})
+        out["calls"] = calls.value
 
 
 class _MatmulFn(torch.autograd.Function):

@@ -1,10 +1,11 @@
 """Row-sharded matrix product over the GPUs of one node.
 
 A is split into contiguous row blocks, one per rank; B is replicated; every rank runs the whole
-Strassen pipeline of libb200s.so on its (M/P) x K block and the bf16 row blocks of C are exchanged
-with one all-gather (NCCL over NVLink on GPUs). Row panels let the gather of panel i overlap the
-product of panel i+1. The reference has no multi-GPU product; this is the partition its
-multi-GPU configuration names (M = N = K = 32768 over 1/2/4/8 GPUs).
+product pipeline of libb200s.so on its (M/P) x K block. Two exchanges of the row blocks of C exist:
+``sharded_matmul`` gathers them with an all-gather (NCCL over NVLink on GPUs; row panels let the
+gather of panel i overlap the product of panel i+1), ``PeerShardedMatmul`` stores every finished tile
+into all ranks' copies of C from the product kernels themselves. The reference has no multi-GPU
+product; this is the partition its multi-GPU configuration names (M = N = K = 32768 over 1/2/4/8 GPUs).
 """
 from __future__ import annotations
 
@@ -47,18 +48,25 @@ def sharded_matmul(A_block: torch.Tensor, B: torch.Tensor, M: int, *, group=None
         from . import ops
 
         # One scratch buffer for all panels: B's operand blocks are formed by the first panel and
-        # reused by the later ones of the same extent (b_blocks_ready).
-        state = {"rows": None, "ws": matmul_kwargs.pop("workspace", None)}
+        # reused by the later ones of the same extent (b_blocks_ready). The buffer is sized from the
+        # very problem every call will pose (all keyword arguments included), and the blocks count as
+        # ready only when the previous call really used this buffer for the same B and extent.
+        state = {"key": None, "ws": matmul_kwargs.pop("workspace", None)}
+        names = ("algo", "depth", "beta", "prod_dtype", "precision", "tile_variant", "pipeline", "b_blocks_ready", "fuse")
+        defaults = ("auto", -1, 0, None, None, 0, 0, False, 0)
 
         def matmul_fn(a, b):
             c = torch.empty((a.shape[0], b.shape[-1]), dtype=a.dtype, device=a.device)
-            p, _, _ = ops.make_problem(a, b, c, matmul_kwargs.get("algo", "auto"), matmul_kwargs.get("depth", -1))
+            args = [matmul_kwargs.get(n, d) for n, d in zip(names, defaults)]
+            p, _, _ = ops.make_problem(a, b, c, *args)
             need = ops.workspace_bytes(p)
-            if need and (state["ws"] is None or state["ws"].numel() < need):
-                state["ws"], state["rows"] = torch.empty(need, dtype=torch.uint8, device=a.device), None
-            ready = state["rows"] == a.shape[0] and need > 0
-            ops.matmul_out(a, b, c, b_blocks_ready=ready, workspace=state["ws"], **matmul_kwargs)
-            state["rows"] = a.shape[0]
+            if need and (state["ws"] is None or state["ws"].numel() * state["ws"].element_size() < need):
+                state["ws"], state["key"] = torch.empty(need, dtype=torch.uint8, device=a.device), None
+            key = (a.shape[0], b.data_ptr(), need)
+            ready = need > 0 and state["key"] == key
+            kw = {k: v for k, v in matmul_kwargs.items() if k != "b_blocks_ready"}
+            ops.matmul_out(a, b, c, b_blocks_ready=ready, workspace=state["ws"], **kw)
+            state["key"] = key
             return c
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -121,23 +129,34 @@ def _all_gather_uneven(views, mine, group):
 
 
 class PeerShardedMatmul:
-    """Row-sharded C = A @ B whose exchange is fused into the recombination kernel.
+    """Row-sharded C = A @ B whose exchange rides on the product kernels.
 
     Every rank holds a full-size C in symmetric memory (``torch.distributed._symmetric_memory``:
     each rank's buffer is mapped into every other rank's address space). A rank forms its row block
-    of the product panel by panel; the recombination kernel of a panel (``b200s_combine_peers``)
-    stores each finished vector into all ranks' C at once with plain global stores over NVLink, on a
-    side stream, while the tensor cores already work on the next panel. No all-gather pass and no
-    staging copy remain. With ``exchange="copy"`` the kernel writes only the local C and the copy
-    engines push the finished rows to the peers instead, which holds no SM during the transfer. Two device-side barriers per call order the ranks: nobody overwrites a
-    peer's C before that peer has entered the call, nobody returns before all stores have landed.
+    of the product panel by panel through ``b200s_matmul_peers``: a dense panel stores each finished
+    tile into all ranks' C straight from the GEMM's TMA-store epilogue, a Strassen panel does the same
+    from its recombination kernel - plain stores over NVLink, tile by tile, no all-gather pass and no
+    staging copy; every load reads local memory. ``exchange="push"`` / ``"copy"`` instead write the
+    panel into the local C and send the finished rows with a small copy kernel or the copy engines.
+
+    Algorithm and depth of a panel come from the library's tuner table for the per-rank shape unless
+    given (at eight ranks a 4096 x 32768 x 32768 panel is a dense product: with B replicated its
+    operand sums would be repeated on every rank).
+
+    Two device-side barriers per call order the ranks (``b200s_peer_barrier`` over a symmetric pad of
+    counters): nobody overwrites a peer's C before that peer has entered the call, nobody returns
+    before all stores have landed. The barriers are bounded: a peer that never arrives costs
+    ``barrier_ms`` and shows up in ``check()`` / ``ops.device_status()`` as a timeout, the GPU is not
+    left spinning.
 
     Build it once per shape (allocation and rendezvous are collective and slow), then call it with
     this rank's row block of A and the whole B. The result tensor is reused by every call.
     """
 
-    def __init__(self, M: int, N: int, K: int, dtype=torch.bfloat16, group=None, algo: str = "classic",
-                 depth: int = 2, panels: int = 2, device=None, exchange: str = "store"):
+    def __init__(self, M: int, N: int, K: int, dtype=torch.bfloat16, group=None, algo: str = "auto",
+                 depth: int = -1, panels: int = 1, device=None, exchange: str = "store", barrier_ms: float = 2000.0):
+        import ctypes
+
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _lib, ops
@@ -150,37 +169,70 @@ class PeerShardedMatmul:
             raise ValueError("at most 8 ranks (one node)")
         if M % self.world:
             raise ValueError("M must be a multiple of the number of ranks")
-        if depth not in (1, 2):
-            raise ValueError("depth must be 1 or 2 (a dense product has no recombination to fuse into)")
-        self.M, self.N, self.K, self.dtype, self.algo, self.depth = M, N, K, dtype, algo, depth
         if exchange not in ("store", "copy", "push"):
             raise ValueError("exchange must be 'store', 'push' or 'copy'")
+        self.M, self.N, self.K, self.dtype = M, N, K, dtype
         self.exchange = exchange
         self.rows = M // self.world
-        quantum = 8 << depth
-        if self.rows % quantum or N % quantum or K % quantum:
-            raise ValueError(f"rows per rank, N and K must be multiples of {quantum} at depth {depth}")
-        while panels > 1 and (self.rows % panels or (self.rows // panels) % quantum):
-            panels -= 1
-        self.panels = panels
-        self.prow = self.rows // panels
         self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        # what the library would run for one panel (its tuner table, or the caller's choice) decides
+        # how many panels fit: fewer when the rows of a panel do not split as the depth needs
+        while True:
+            prow = self.rows // panels
+            if self.rows % panels == 0:
+                prob = _lib.Problem()
+                prob.M, prob.N, prob.K, prob.batch = prow, N, K, 1
+                prob.lda, prob.ldb, prob.ldc = K, N, N
+                prob.a_major, prob.b_major = _lib.K_MAJOR, _lib.MN_MAJOR
+                prob.in_dtype = prob.out_dtype = ops._DTYPE[dtype]
+                prob.algo = ops._ALGO[algo]
+                prob.depth, prob.prod_dtype, prob.pipeline, prob.fuse = int(depth), -1, 2, 2
+                try:
+                    a_res, d_res = ops.resolve(prob)
+                    break
+                except ValueError:
+                    pass
+            if panels == 1:
+                raise ValueError(f"rows per rank ({self.rows}), N and K do not fit algo {algo!r} at depth {depth}")
+            panels -= 1
+        self.panels, self.prow = panels, self.rows // panels
+        self.algo = {_lib.ALGO_DENSE: "dense", _lib.ALGO_CLASSIC: "classic", _lib.ALGO_WINOGRAD: "winograd"}[a_res]
+        self.depth = d_res
+        if self.depth > 2:
+            raise ValueError("a panel runs dense or as one pipeline of up to two levels")
+        if (N * torch.empty((), dtype=dtype).element_size()) % 16:
+            raise ValueError("rows of C must be a multiple of 16 bytes long")
         self.C = symm_mem.empty((M, N), dtype=dtype, device=self.device)
         self.hdl = symm_mem.rendezvous(self.C, self.group.group_name)
         self.peer_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
-        es = self.C.element_size()
-        div, P = 1 << depth, 7 ** depth
-        self.P, self.Mb, self.Nb, self.Kb = P, self.prow // div, N // div, K // div
-        self.sa = torch.empty(P * self.Mb * self.Kb, dtype=dtype, device=self.device)
-        self.sb = torch.empty(P * self.Kb * self.Nb, dtype=dtype, device=self.device)
-        self.mp = [torch.empty((P, self.Mb, self.Nb), dtype=dtype, device=self.device) for _ in range(min(2, panels))]
-        # products on a high-priority stream, the NVLink-bound recombination on a low-priority one
-        self.hi = torch.cuda.Stream(self.device, priority=-1)
-        self.side = torch.cuda.Stream(self.device, priority=0)
-        self.copy_streams = [torch.cuda.Stream(self.device) for _ in range(self.world)]
-        self.ev_gemm = [torch.cuda.Event() for _ in range(panels)]
-        self.ev_comb = [torch.cuda.Event() for _ in range(panels)]
-        self._es = es
+        self.pad = symm_mem.empty((64,), dtype=torch.int32, device=self.device)
+        self.pad.zero_()
+        torch.cuda.synchronize(self.device)
+        pad_hdl = symm_mem.rendezvous(self.pad, self.group.group_name)
+        dist.barrier(self.group)          # every pad is zero before the first device-side barrier
+        self._pads = (ctypes.c_void_p * self.world)(*[int(p) for p in pad_hdl.buffer_ptrs])
+        self._epoch = 0
+        self._limit_ns = int(barrier_ms * 1e6)
+        self._es = self.C.element_size()
+        self._ws = None
+        self.copy_streams = [torch.cuda.Stream(self.device) for _ in range(self.world)] if exchange == "copy" else []
+        self.ev_panel = [torch.cuda.Event() for _ in range(panels)]
+
+    def _barrier(self, stream):
+        self._epoch += 1
+        self._lib.check(self._lib.load().b200s_peer_barrier(self._pads, self.rank, self.world, self._epoch,
+                                                            self._limit_ns, stream.cuda_stream))
+
+    def panel_product(self, a_panel: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+        """The product of one row panel as this plan computes it, into fresh local memory: the same
+        kernels and arithmetic as the exchanged panel, for checking what arrived bit for bit."""
+        return self._ops.matmul(a_panel, B, algo=self.algo, depth=self.depth, pipeline=2, fuse=2)
+
+    def check(self) -> None:
+        """Synchronises and raises if a device-side wait (a barrier, a kernel role) gave up."""
+        status, detail = self._ops.device_status(self.device)
+        if status != 0:
+            raise self._lib.B200SError(status, f"{self._lib.status_string(status)} (waiter {detail})")
 
     def __call__(self, A_block: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
         import ctypes
@@ -188,72 +240,45 @@ class PeerShardedMatmul:
         lib, ops = self._lib.load(), self._ops
         if A_block.shape != (self.rows, self.K) or B.shape != (self.K, self.N):
             raise ValueError("operand shapes do not match the plan")
-        user = torch.cuda.current_stream(self.device)
-        main = self.hi
-        P, Mb, Nb, Kb = self.P, self.Mb, self.Nb, self.Kb
-        self.hdl.barrier(channel=0)          # every rank is done with the previous contents of C
-        main.wait_stream(user)
-        first = None
+        stream = torch.cuda.current_stream(self.device)
+        self._barrier(stream)                # every rank is done with the previous contents of C
         for i in range(self.panels):
             p0 = i * self.prow
             a_panel = A_block[p0:p0 + self.prow]
-            c_rows = self.C[self.rank * self.rows + p0: self.rank * self.rows + p0 + self.prow]
-            prob, a2, b2 = ops.make_problem(a_panel, B, c_rows, self.algo, self.depth)
-            a_k, b_k = prob.a_major == self._lib.K_MAJOR, prob.b_major == self._lib.K_MAJOR
-            with torch.cuda.stream(main):
-                if first is None:
-                    first = prob
-                    self._lib.check(lib.b200s_preadd(ctypes.byref(prob), 1, b2.data_ptr(), self.sb.data_ptr(),
-                                                     main.cuda_stream))
-                self._lib.check(lib.b200s_preadd(ctypes.byref(prob), 0, a2.data_ptr(), self.sa.data_ptr(),
-                                                 main.cuda_stream))
-                sa = self.sa.view(P, Mb, Kb) if a_k else self.sa.view(P, Kb, Mb).transpose(1, 2)
-                sb = self.sb.view(P, Nb, Kb).transpose(1, 2) if b_k else self.sb.view(P, Kb, Nb)
-                mp = self.mp[i % len(self.mp)]
-                if i >= len(self.mp):
-                    main.wait_event(self.ev_comb[i - len(self.mp)])   # that recombination still reads this buffer
-                ops.matmul_out(sa, sb, mp, algo="dense")
-                self.ev_gemm[i].record(main)
-            with torch.cuda.stream(self.side):
-                self.side.wait_event(self.ev_gemm[i])
-                row0 = self.rank * self.rows + p0
-                if self.exchange == "store":
-                    # one kernel: recombine and store every vector into all ranks' C over NVLink
-                    dst = (ctypes.c_void_p * self.world)(*[ptr + row0 * self.N * self._es for ptr in self.peer_ptrs])
-                    self._lib.check(lib.b200s_combine_peers(ctypes.byref(prob), mp.data_ptr(), dst, self.world,
-                                                            self.side.cuda_stream))
-                    self.ev_comb[i].record(self.side)
-                elif self.exchange == "push":
-                    # recombine into the local C at full occupancy, then a small-footprint kernel that
-                    # fits beside the next panel's GEMM CTAs stores the rows into the peers' C
-                    self._lib.check(lib.b200s_combine(ctypes.byref(prob), mp.data_ptr(), c_rows.data_ptr(),
-                                                      self.side.cuda_stream))
-                    self.ev_comb[i].record(self.side)
-                    if self.world > 1:
-                        peers = [ptr + row0 * self.N * self._es for r, ptr in enumerate(self.peer_ptrs) if r != self.rank]
-                        dst = (ctypes.c_void_p * len(peers))(*peers)
-                        self._lib.check(lib.b200s_push_rows(c_rows.data_ptr(), dst, len(peers),
-                                                            self.prow * self.N * self._es, self.side.cuda_stream))
-                else:
-                    # recombine into the local C, then let the copy engines push the finished rows to
-                    # the peers: no SM is held while the bytes cross NVLink
-                    self._lib.check(lib.b200s_combine(ctypes.byref(prob), mp.data_ptr(), c_rows.data_ptr(),
-                                                      self.side.cuda_stream))
-                    self.ev_comb[i].record(self.side)
-                    for r in range(self.world):
-                        if r != self.rank:
-                            # one stream per peer, so the transfers to different peers run side by side
-                            cs = self.copy_streams[r]
-                            cs.wait_event(self.ev_comb[i])
-                            with torch.cuda.stream(cs):
-                                peer_rows = self.hdl.get_buffer(r, (self.prow, self.N), self.dtype, row0 * self.N)
-                                peer_rows.copy_(c_rows, non_blocking=True)
-        user.wait_stream(main)
-        user.wait_stream(self.side)
-        if self.exchange == "copy":
-            for cs in self.copy_streams:
-                user.wait_stream(cs)
-        for t in (A_block, B):
-            t.record_stream(main)
-        self.hdl.barrier(channel=1)          # every rank's stores have been issued and completed
+            row0 = self.rank * self.rows + p0
+            c_rows = self.C[row0: row0 + self.prow]
+            prob, a2, b2 = ops.make_problem(a_panel, B, c_rows, self.algo, self.depth, pipeline=2, fuse=2,
+                                            b_blocks_ready=i > 0 and self.depth > 0)
+            need = ops.workspace_bytes(prob)
+            if need and (self._ws is None or self._ws.numel() < need):
+                if i > 0:
+                    raise RuntimeError("scratch of a later panel larger than the first panel's")
+                self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            ws_ptr = self._ws.data_ptr() if need else None
+            if self.exchange == "store":
+                dst = (ctypes.c_void_p * self.world)(*[ptr + row0 * self.N * self._es for ptr in self.peer_ptrs])
+                self._lib.check(lib.b200s_matmul_peers(ctypes.byref(prob), a2.data_ptr(), b2.data_ptr(), dst, self.world,
+                                                       ws_ptr, need, stream.cuda_stream))
+                continue
+            self._lib.check(lib.b200s_matmul(ctypes.byref(prob), a2.data_ptr(), b2.data_ptr(), c_rows.data_ptr(), ws_ptr,
+                                             need, stream.cuda_stream))
+            if self.world == 1:
+                continue
+            nbytes = self.prow * self.N * self._es
+            if self.exchange == "push":
+                peers = [ptr + row0 * self.N * self._es for r, ptr in enumerate(self.peer_ptrs) if r != self.rank]
+                dst = (ctypes.c_void_p * len(peers))(*peers)
+                self._lib.check(lib.b200s_push_rows(c_rows.data_ptr(), dst, len(peers), nbytes, stream.cuda_stream))
+            else:
+                self.ev_panel[i].record(stream)
+                for r in range(self.world):
+                    if r != self.rank:
+                        cs = self.copy_streams[r]     # one stream per peer: the transfers run side by side
+                        cs.wait_event(self.ev_panel[i])
+                        with torch.cuda.stream(cs):
+                            peer_rows = self.hdl.get_buffer(r, (self.prow, self.N), self.dtype, row0 * self.N)
+                            peer_rows.copy_(c_rows, non_blocking=True)
+        for cs in self.copy_streams:
+            stream.wait_stream(cs)
+        self._barrier(stream)                # every rank's stores have been issued and completed
         return self.C

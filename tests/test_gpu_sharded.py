@@ -33,8 +33,8 @@ def single_rank_group(built_library):
 
 
 @pytest.mark.parametrize("exchange", ["store", "push", "copy"])
-@pytest.mark.parametrize("panels", [1, 2])
-def test_peer_sharded_plan_single_rank(single_rank_group, exchange, panels):
+@pytest.mark.parametrize("algo,depth,panels", [("classic", 2, 1), ("classic", 2, 2), ("dense", 0, 2), ("winograd", 1, 1)])
+def test_peer_sharded_plan_single_rank(single_rank_group, exchange, algo, depth, panels):
     from strassen_triton_b200 import ops
     from strassen_triton_b200.sharded import PeerShardedMatmul
 
@@ -42,19 +42,58 @@ def test_peer_sharded_plan_single_rank(single_rank_group, exchange, panels):
     A, B = seeded_pair(77, (M, K), (K, N), dist="uniform")
     A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
     try:
-        plan = PeerShardedMatmul(M, N, K, torch.bfloat16, group=single_rank_group, algo="classic", depth=2,
-                                 panels=panels, exchange=exchange)
+        plan = PeerShardedMatmul(M, N, K, torch.bfloat16, group=single_rank_group, algo=algo, depth=depth,
+                                 panels=panels, exchange=exchange, barrier_ms=200)
     except RuntimeError as e:  # symmetric memory not available in this environment
         pytest.skip(f"symmetric memory rendezvous unavailable: {e}")
+    assert (plan.algo, plan.depth, plan.panels) == (algo, depth, panels)
     for _ in range(2):
         C = plan(A, B)
-    torch.cuda.synchronize()
+    plan.check()
     pr = plan.prow
-    want = torch.cat([ops.matmul(A[i * pr:(i + 1) * pr], B, algo="classic", depth=2) for i in range(M // pr)])
+    want = torch.cat([plan.panel_product(A[i * pr:(i + 1) * pr], B) for i in range(M // pr)])
     assert torch.equal(C, want)
     ref = A.double() @ B.double()
     assert ((C.double() - ref).norm() / ref.norm()).item() < 2e-2
     assert ops.device_status() == (0, 0)
+
+
+def test_peer_barrier_gives_up_on_a_rank_that_never_arrives(single_rank_group):
+    """Two pads, this process plays rank 0, nobody plays rank 1: the barrier waits its limit, reports
+    the timeout with its own waiter code and returns; the next launch on the device works."""
+    import ctypes
+
+    from strassen_triton_b200 import _lib, ops
+
+    lib = _lib.load()
+    pads = torch.zeros(2, 64, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(pads[0].data_ptr(), pads[1].data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.b200s_peer_barrier(ptrs, 0, 2, 1, 5_000_000, stream) == 0          # 5 ms
+    assert ops.device_status() == (_lib.ERR_DEVICE_TIMEOUT, 8)
+    assert pads[1, 0].item() == 1 and pads[0, 0].item() == 1                     # it did signal both pads
+    assert ops.device_status() == (0, 0)
+    # with the missing rank's slots filled in by hand the same barrier passes
+    pads[0, 1] = 2
+    assert lib.b200s_peer_barrier(ptrs, 0, 2, 2, 5_000_000, stream) == 0
+    assert ops.device_status() == (0, 0)
+    assert lib.b200s_peer_barrier(ptrs, 2, 2, 3, 5_000_000, stream) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_peer_barrier(None, 0, 2, 3, 5_000_000, stream) == _lib.ERR_NULL_POINTER
+
+
+def test_nccl_gather_with_fp32_products_across_panels(single_rank_group):
+    """Several panels with keyword arguments that change the scratch size: the shared buffer is sized
+    for the real problem and B's blocks are reused only when they are really there."""
+    from strassen_triton_b200 import ops
+    from strassen_triton_b200.sharded import sharded_matmul
+
+    M, N, K = 1024, 512, 512
+    A, B = seeded_pair(79, (M, K), (K, N), dist="uniform")
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    C = sharded_matmul(A, B, M, group=single_rank_group, panels=4, algo="classic", depth=2, prod_dtype=torch.float32)
+    want = torch.cat([ops.matmul(A[256 * i:256 * (i + 1)], B, algo="classic", depth=2, prod_dtype=torch.float32)
+                      for i in range(4)])
+    assert torch.equal(C, want)
 
 
 def test_nccl_sharded_matmul_single_rank(single_rank_group):
