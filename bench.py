@@ -3,17 +3,32 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-One "step" is one full product C = A @ B through the library's public entry
-(``fixed_strassen_fp32_agg.strassen_matmul_n_layers`` semantics: two Strassen levels, bf16
-operands, fp32 accumulation and aggregation, bf16 result).
+One "step" is one full product C = A @ B through the library (two Strassen levels where the tuner
+table picks them, bf16 operands, fp32 accumulation and aggregation, bf16 result).
 
 * N = 1: M = N = K = 16384, inputs U(-1,1) from seed 0 (the configuration the headline metric is
-  quoted on). Inputs are resident in HBM for ``value``; ``e2e`` times the same call with pinned host
-  buffers, the host->device copies of A and B and the device->host copy of C inside the timed region.
-* N > 1 (launched by torch.distributed.run, one rank per GPU): M = N = K = 32768, A split into
-  row blocks, B replicated, all-gather of C (NCCL). Total work is fixed: scaling "strong".
-* ``--impl reference``: the reference's own recursion restated for the CPU (``oracle/``), on the host
-  cores, each step a bounded sample (an 8192^3 two-level product) of the same workload.
+  quoted on), algorithm classic / depth 2, schedule from the library's tuner table. ``value`` times
+  K steps with the inputs resident in HBM; ``e2e`` times the same product through
+  ``fixed_strassen_fp32_agg.strassen_matmul_n_layers`` with pinned host buffers and all three copies
+  inside the timed region. ``interleaved`` is the comparison with cuBLAS dense on the same GPU: the
+  two arms alternate (A B A B ...), every turn starts on a rested GPU and runs back to back for
+  ``--seconds``; the first 20 calls of a turn are its "burst" figure, the last second its "sustained"
+  one, each with the SM clock sampled during the turn. ``reference_gpu`` is the reference recursion
+  (the oracle port) on CUDA tensors, i.e. the reference as it would run on this GPU with cuBLAS
+  sub-products. ``stages_ms`` comes from the library's own stage events recorded during the K timed
+  steps.
+* N > 1 (launched by torch.distributed.run, one rank per GPU): M = N = K = 32768, A split into row
+  blocks, B replicated; every rank runs the algorithm the tuner table picks for its block and stores
+  every finished tile into all ranks' C over NVLink from the product kernel itself (peer stores; no
+  NCCL collective in the timed path; ``--exchange nccl`` gathers with an NCCL all-gather instead).
+  Total work is fixed: scaling "strong". After the timed region every rank recomputes row panels that
+  other ranks own and compares them bit for bit with what arrived (``verify``); a mismatch ends the
+  run with a non-zero exit code. Then a GPT-2-124M FSDP train step with every Linear through the
+  library is timed (``fsdp_step``) and checked against an nn.Linear twin (``fsdp_twin_ok``).
+* ``--impl reference``: the reference's own recursion restated for the CPU (``oracle/``) on the host
+  cores; ``config`` states the product it really multiplies and ``stands_for`` the workload it samples.
+* ``--only CASE``: runs one kernel of the pipeline a few times on synthetic data and exits (for
+  profiling one kernel under ncu): gemm_grouped, dense, preadd, combine, fused.
 
 Prints one JSON line (rank 0).
 """
@@ -37,9 +52,12 @@ import torch  # noqa: E402
 METRIC = "effective TFLOP/s (2MNK/t) bf16 Strassen"
 UNIT = "TFLOP/s"
 
-# DRAM bytes (read + write) of one launch of the grouped GEMM kernel on the N=1 workload, from
-# the ncu launch list summarised in profiles/bench_16384_depth2_launch_list.md.
-GEMM_DRAM_TRAFFIC_BYTES = 9.58e9
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the product kernel on a
+# one-kernel ncu capture of 14 products of 4096^3; a full launch of the N = 1 workload runs 49 such
+# products and its traffic grows in proportion.
+GEMM_DRAM_BYTES_14_PRODUCTS = 1.549e9 + 0.450e9
+GEMM_DRAM_SOURCE = ("ncu one-kernel capture, 14 products of 4096^3 (1.549 GB read + 0.450 GB written), "
+                    "scaled by 49/14 to the 49 products of a launch")
 
 
 def measured_peaks():
@@ -53,16 +71,17 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 50 ms while the timed region runs."""
+    """Samples nvidia-smi clocks, power and throttle reasons every 50 ms, with host timestamps."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines = []
+        self.rows = []      # (host time, sm MHz, max MHz, watts, set of active reasons)
 
     def start(self):
         try:
@@ -72,50 +91,56 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        sm, smax, power, reasons = [], [], [], set()
-        for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
             try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-                power.append(float(parts[3]))
+                row = (time.time(), float(parts[1]), float(parts[2]), float(parts[3]),
+                       {n for n, v in zip(self.NAMES, parts[5:9]) if v.lower().startswith("active")})
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+            self.rows.append(row)
+
+    def window(self, t0, t1):
+        """Summary of the samples taken between two host times."""
+        rows = [r for r in self.rows if t0 <= r[0] <= t1]
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(smax), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons)}
+        sm = sorted(r[1] for r in rows)
+        reasons = set()
+        for r in rows:
+            reasons |= r[4]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(r[2] for r in rows),
+                "power_w_max": max(r[3] for r in rows), "samples": len(rows), "reasons": sorted(reasons)}
+
+    def stop(self):
+        if self.proc is None:
+            return
+        time.sleep(0.1)
+        self.proc.terminate()
 
 
-def seeded_inputs(n_rows_a, n, dist, seed, device, row_offset=0, total_rows=None):
+def seeded_inputs(n_rows_a, n, dist, seed, device, row_offset=0, want_b=True):
     """A (rows [row_offset, row_offset + n_rows_a) of the full M x K matrix) and B (K x N), bf16.
     Generated on the device from seeded generators: synthetic data with the configuration's
-    distribution (the parity tests use CPU-generated inputs; throughput does not depend on bits)."""
+    distribution (the parity tests use CPU-generated inputs; throughput does not depend on bits).
+    The rows of A depend only on (seed, row_offset, n_rows_a), so any rank can regenerate any block."""
     g = torch.Generator(device=device).manual_seed(seed + 7919 * row_offset)
     gb = torch.Generator(device=device).manual_seed(seed + 1)
+    B = None
     if dist == "uniform":
         A = torch.rand((n_rows_a, n), generator=g, device=device) * 2 - 1
-        B = torch.rand((n, n), generator=gb, device=device) * 2 - 1
+        if want_b:
+            B = torch.rand((n, n), generator=gb, device=device) * 2 - 1
     else:
         A = torch.randn((n_rows_a, n), generator=g, device=device) / n ** 0.5
-        B = torch.randn((n, n), generator=gb, device=device) / n ** 0.5
-    return A.bfloat16(), B.bfloat16()
+        if want_b:
+            B = torch.randn((n, n), generator=gb, device=device) / n ** 0.5
+    return A.bfloat16(), (B.bfloat16() if want_b else None)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -152,14 +177,17 @@ def cpu_baseline(budget_s=25.0):
 
 
 def run_reference_arm(args):
+    """The reference recursion on the host cores. `config` carries the product that is really
+    multiplied; when that is smaller than the workload of the GPU arm, `stands_for` names the latter."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    n = 8192
-    probe, A, B = cpu_reference_step(2048, 2)
-    # keep the whole run within a few minutes on slow hosts
+    full = 16384 if args.gpus == 1 else 32768
+    probe, _, _ = cpu_reference_step(2048, 2)
+    n = full
+    # keep the whole run within a few minutes: the cost grows with n^3
     while n > 2048 and probe * (n / 2048) ** 3 * (args.steps + args.warmup) > 240:
         n //= 2
     g = torch.Generator("cpu").manual_seed(0)
@@ -172,12 +200,18 @@ def run_reference_arm(args):
         cpu_reference_step(n, 2, A, B)
     dt = time.perf_counter() - t0
     value = 2 * n ** 3 * args.steps / dt / 1e12
-    sample = f"each step one {n}^3 two-level bf16 product of the reference recursion (oracle port) on {cores} host threads"
+    sample = (f"each step one {n}^3 two-level bf16 product of the reference recursion (oracle port) on {cores} "
+              "host threads")
+    config = {"workload": f"two-level Strassen C=A.B, M=N=K={n}, bf16 inputs U(-1,1) seed 0, the reference recursion "
+                          "(fixed_strassen_fp32_agg.strassen_matmul_n_layers as shipped) through torch on the host cores",
+              "M": n, "N": n, "K": n, "depth": 2, "algo": "classic"}
+    if n != full:
+        config["stands_for"] = workload_config(args.gpus)["workload"]
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": config,
         "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -191,9 +225,10 @@ def workload_config(n_gpus):
                             "and aggregation, bf16 output (the headline configuration)",
                 "M": 16384, "N": 16384, "K": 16384, "depth": 2, "algo": "classic",
                 "l2": "inputs (1.6 GB) exceed L2 (126 MB); no flush between steps"}
-    return {"workload": f"row-sharded two-level Strassen, M=N=K=32768, bf16 inputs N(0,1)/sqrt(K), A in {n_gpus} row "
-                        "blocks, B replicated, every rank ends with the whole C (the multi-GPU configuration)",
-            "M": 32768, "N": 32768, "K": 32768, "depth": 2, "algo": "classic", "parallelism": f"rowshard{n_gpus}",
+    return {"workload": f"row-sharded product, M=N=K=32768, bf16 inputs N(0,1)/sqrt(K), A in {n_gpus} row "
+                        "blocks, B replicated, every rank ends with the whole C (the multi-GPU configuration); "
+                        "per-rank algorithm from the tuner table",
+            "M": 32768, "N": 32768, "K": 32768, "parallelism": f"rowshard{n_gpus}",
             "l2": "inputs exceed L2 (126 MB); no flush between steps"}
 
 
@@ -216,36 +251,179 @@ def timed(fn, steps, sync, barrier):
     return e0.elapsed_time(e1)
 
 
-def stage_breakdown(ops, _lib, A, B, C, depth, steps):
-    """Average duration of each kernel of the pipeline, driven through the stand-alone C-ABI
-    passes with CUDA events between them on the launching stream."""
-    lib = _lib.load()
-    p, A2, B2 = ops.make_problem(A, B, C, "classic", depth)
-    need = ops.workspace_bytes(p)
-    ws = torch.empty(need, dtype=torch.uint8, device=A.device)
-    M, N, K = p.M, p.N, p.K
-    div, np_ = 1 << depth, 7 ** depth
-    Mb, Nb, Kb = M // div, N // div, K // div
-    sa = ws[: np_ * Mb * Kb * 2].view(torch.bfloat16).view(np_, Mb, Kb)
-    off = (np_ * Mb * Kb * 2 + 255) // 256 * 256
-    sb = ws[off: off + np_ * Kb * Nb * 2].view(torch.bfloat16).view(np_, Kb, Nb)
-    off2 = off + (np_ * Kb * Nb * 2 + 255) // 256 * 256
-    mp = ws[off2: off2 + np_ * Mb * Nb * 2].view(torch.bfloat16).view(np_, Mb, Nb)
-    stream = torch.cuda.current_stream().cuda_stream
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
-    for s in range(steps):
-        ev[s][0].record()
-        _lib.check(lib.b200s_preadd(ctypes.byref(p), 0, A2.data_ptr(), sa.data_ptr(), stream))
-        ev[s][1].record()
-        _lib.check(lib.b200s_preadd(ctypes.byref(p), 1, B2.data_ptr(), sb.data_ptr(), stream))
-        ev[s][2].record()
-        ops.matmul_out(sa, sb, mp, algo="dense")
-        ev[s][3].record()
-        _lib.check(lib.b200s_combine(ctypes.byref(p), mp.data_ptr(), C.data_ptr(), stream))
-        ev[s][4].record()
+def one_turn(fn, seconds, sampler, chunk=20):
+    """One turn of an arm: back-to-back calls for `seconds` from a rested GPU, an event every `chunk`
+    calls. Returns the ms per call of the first chunk (burst), of the last second (sustained) and the
+    SM clock sampled during the turn."""
     torch.cuda.synchronize()
-    names = ["preadd_A", "preadd_B", "gemm_grouped", "combine"]
-    return {n: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) / steps for i, n in enumerate(names)}
+    time.sleep(0.5)
+    events = [torch.cuda.Event(enable_timing=True)]
+    t0 = time.time()
+    events[0].record()
+    while True:
+        for _ in range(chunk):
+            fn()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        events.append(e)
+        if len(events) > 3:
+            events[-3].synchronize()        # at most two chunks queued ahead
+        if time.time() - t0 >= seconds:
+            break
+    torch.cuda.synchronize()
+    t1 = time.time()
+    per_chunk = [events[i].elapsed_time(events[i + 1]) / chunk for i in range(len(events) - 1)]
+    tail, acc = [], 0.0
+    for ms in reversed(per_chunk):
+        tail.append(ms)
+        acc += ms * chunk
+        if acc >= 1000.0:
+            break
+    clk = sampler.window(t0 + 0.2, t1) if sampler else {"sm_mhz": None}
+    return {"burst_ms": per_chunk[0], "sustained_ms": sum(tail) / len(tail), "calls": chunk * len(per_chunk),
+            "sm_mhz": clk.get("sm_mhz"), "reasons": clk.get("reasons", [])}
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
+
+
+def interleaved(arms, rounds, seconds, sampler, flops):
+    """A B A B ... turns; per arm the list of burst and sustained figures and their medians."""
+    out = {name: {"burst_ms": [], "sustained_ms": [], "sm_mhz": []} for name in arms}
+    for _ in range(rounds):
+        for name, fn in arms.items():
+            r = one_turn(fn, seconds, sampler)
+            out[name]["burst_ms"].append(round(r["burst_ms"], 4))
+            out[name]["sustained_ms"].append(round(r["sustained_ms"], 4))
+            out[name]["sm_mhz"].append(r["sm_mhz"])
+    for name, d in out.items():
+        d["burst_ms_median"] = round(median(d["burst_ms"]), 4)
+        d["sustained_ms_median"] = round(median(d["sustained_ms"]), 4)
+        d["burst_tflops"] = round(flops / (d["burst_ms_median"] * 1e-3) / 1e12, 1)
+        d["sustained_tflops"] = round(flops / (d["sustained_ms_median"] * 1e-3) / 1e12, 1)
+        mhz = [m for m in d["sm_mhz"] if m]
+        if mhz:
+            # clock-normalised cost: milliseconds x MHz of the sustained second
+            d["sustained_ms_x_mhz"] = round(d["sustained_ms_median"] * median(mhz), 1)
+    return out
+
+
+def run_only(args):
+    """One kernel of the pipeline a few times on synthetic data (for one-kernel profiling)."""
+    from strassen_triton_b200 import _lib, ops
+
+    lib = _lib.load()
+    what, n, nb = args.only, args.n, args.products
+    stream = torch.cuda.current_stream().cuda_stream
+    if what == "gemm_grouped":
+        A = torch.randn(nb, n, n, device="cuda").bfloat16()
+        B = torch.randn(nb, n, n, device="cuda").bfloat16()
+        C = torch.empty_like(A)
+        for _ in range(args.steps):
+            ops.matmul_out(A, B, C, algo="dense")
+    elif what == "dense":
+        A = torch.randn(n, n, device="cuda").bfloat16()
+        B = torch.randn(n, n, device="cuda").bfloat16()
+        C = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+        for _ in range(args.steps):
+            ops.matmul_out(A, B, C, algo="dense")
+    elif what in ("preadd", "combine"):
+        A = (torch.rand(n, n, device="cuda") * 2 - 1).bfloat16()
+        C = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+        p, _, _ = ops.make_problem(A, A, C, "classic", 2)
+        blocks = torch.randn(49, n // 4, n // 4, device="cuda").bfloat16()
+        for _ in range(args.steps):
+            if what == "preadd":
+                _lib.check(lib.b200s_preadd(ctypes.byref(p), 0, A.data_ptr(), blocks.data_ptr(), stream))
+            else:
+                _lib.check(lib.b200s_combine(ctypes.byref(p), blocks.data_ptr(), C.data_ptr(), stream))
+    elif what == "fused":
+        A = (torch.rand(n, n, device="cuda") * 2 - 1).bfloat16()
+        B = (torch.rand(n, n, device="cuda") * 2 - 1).bfloat16()
+        C = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+        for _ in range(args.steps):
+            ops.matmul_out(A, B, C, algo="classic", depth=2, fuse=3)
+    else:
+        raise SystemExit(f"unknown --only case {what!r}")
+    torch.cuda.synchronize()
+    print(json.dumps({"only": what, "n": n, "products": nb, "steps": args.steps, "device_status": ops.device_status()}))
+
+
+def verify_sharded(plan, B, n, world, rank, dev, dist):
+    """Every rank recomputes row panels that OTHER ranks own (A's rows are regenerable from the seed,
+    B is replicated) with the same per-panel product, and compares them bit for bit with the rows that
+    arrived in its copy of C; one panel is also checked against fp64 through a probe vector."""
+    from strassen_triton_b200.sharded import row_block
+
+    C = plan.C
+    owners = sorted({(rank + 1) % world, (rank + world // 2) % world} - {rank})
+    rows_checked, exact = 0, True
+    probe_err = 0.0
+    for owner in owners:
+        r0, r1 = row_block(n, world, owner)
+        A_owner, _ = seeded_inputs(r1 - r0, n, "normal", 0, dev, row_offset=r0, want_b=False)
+        for pi in sorted({0, plan.panels - 1}):
+            p0 = pi * plan.prow
+            want = plan.panel_product(A_owner[p0:p0 + plan.prow], B)
+            got = C[r0 + p0: r0 + p0 + plan.prow]
+            exact = exact and bool(torch.equal(got, want))
+            rows_checked += plan.prow
+            if owner == owners[0] and pi == 0:
+                # C x = A (B x) in fp64 on the first rows of this panel
+                x = torch.randn(n, 1, device=dev, dtype=torch.float64)
+                k = min(plan.prow, 2048)
+                ref = A_owner[p0:p0 + k].double() @ _b_times_x(B, x)
+                probe_err = ((got[:k].double() @ x - ref).norm() / ref.norm()).item()
+        del A_owner
+    flag = torch.tensor([1 if exact else 0, rows_checked], device=dev, dtype=torch.int64)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    err = torch.tensor([probe_err], device=dev, dtype=torch.float64)
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    return {"rows_checked_per_rank": int(flag[1].item()), "panels_of_ranks": "rank+1 and rank+world/2",
+            "bit_exact": bool(flag[0].item()), "rel_fro_probe": round(err.item(), 6),
+            "how": "rows stored by other ranks into this rank's C against the same panel product recomputed here"}
+
+
+def _b_times_x(B, x):
+    """B @ x in fp64 without holding all of B in fp64: slabs of 4096 rows at a time."""
+    out = torch.empty(B.shape[0], 1, device=B.device, dtype=torch.float64)
+    for i in range(0, B.shape[0], 4096):
+        out[i:i + 4096] = B[i:i + 4096].double() @ x
+    return out
+
+
+def fsdp_leg(world, rank, dev, dist):
+    """GPT-2-124M FSDP train step with every Linear through the library, and a two-layer twin check
+    against nn.Linear (same weights, same tokens, one forward/backward under FSDP)."""
+    from strassen_triton_b200 import _lib, fsdp_gpt2
+
+    lib = _lib.load()
+    torch.manual_seed(0)
+    model = fsdp_gpt2.build(layers=12, seq=1024, depth=None, device="cuda", world=world)
+    fsdp_gpt2.train_steps(model, 2, batch=8, seq=1024, rank=rank)
+    torch.cuda.synchronize()
+    dist.barrier()
+    n0 = lib.b200s_launch_count()
+    t0 = time.perf_counter()
+    steps = 3
+    losses = fsdp_gpt2.train_steps(model, steps, batch=8, seq=1024, rank=rank)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dt = (time.perf_counter() - t0) / steps
+    launches = (lib.b200s_launch_count() - n0) // steps
+    del model
+    torch.cuda.empty_cache()
+    twin_ok, twin = fsdp_gpt2.twin_check(world, rank)
+    t = torch.tensor([dt], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = torch.tensor([1 if twin_ok else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return {"ms": round(t.item() * 1e3, 2), "tokens_per_s": round(world * 8 * 1024 / t.item()),
+            "library_launches_per_step": int(launches), "loss0": round(losses[0], 4),
+            "model": "GPT-2-124M (12 layers, d 768, 12 heads, vocab 50257 padded to 50304, seq 1024, 8 seqs/GPU), "
+                     "FSDP bf16 mixed precision, AdamW, random tokens", "twin": twin}, bool(ok.item())
 
 
 def run_gpu_arm(args):
@@ -269,6 +447,8 @@ def run_gpu_arm(args):
     lib = _lib.load()
     peaks = measured_peaks()
     depth = 2
+    warmup = max(args.warmup, 3)
+    plan = None
 
     if world == 1:
         n = 16384
@@ -276,37 +456,40 @@ def run_gpu_arm(args):
         C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         p, _, _ = ops.make_problem(A, B, C, "classic", depth)
         ws = torch.empty(ops.workspace_bytes(p), dtype=torch.uint8, device=dev)
-        step = lambda: ops.matmul_out(A, B, C, algo="classic", depth=depth, workspace=ws)  # noqa: E731
-        flops = 2.0 * n ** 3
+        fuse = {"auto": 0, "fused_all": 1, "separate": 2, "fused": 3}[args.schedule]
+        pipe = 2 if fuse == 2 else 0
+        step = lambda: ops.matmul_out(A, B, C, algo="classic", depth=depth, fuse=fuse, pipeline=pipe,  # noqa: E731
+                                      workspace=ws)
     else:
         n = 32768
         r0, r1 = row_block(n, world, rank)
         A, B = seeded_inputs(r1 - r0, n, "normal", 0, dev, row_offset=r0)
-        C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
-        p, _, _ = ops.make_problem(A, B, C[r0:r1], "classic", depth)
-        ws = torch.empty(ops.workspace_bytes(p), dtype=torch.uint8, device=dev)
         if args.exchange.startswith("peer"):
             from strassen_triton_b200.sharded import PeerShardedMatmul
 
-            del C, ws
-            plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo="classic", depth=depth, panels=args.panels,
-                                     device=dev, exchange={"peer": "store", "peer_push": "push", "peer_copy": "copy"}[args.exchange])
+            plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
+                                     panels=args.panels, device=dev,
+                                     exchange={"peer": "store", "peer_push": "push", "peer_copy": "copy"}[args.exchange])
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
         else:
-            step = lambda: sharded_matmul(A, B, n, panels=args.panels, out=C, algo="classic", depth=depth,  # noqa: E731
-                                          workspace=ws)
-        flops = 2.0 * n ** 3
+            C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
+            p, _, _ = ops.make_problem(A, B, C[r0:r1], args.algo, -1 if args.algo == "auto" else depth)
+            ws = torch.empty(max(ops.workspace_bytes(p), 1), dtype=torch.uint8, device=dev)
+            step = lambda: sharded_matmul(A, B, n, panels=args.panels, out=C, algo=args.algo,  # noqa: E731
+                                          depth=-1 if args.algo == "auto" else depth, workspace=ws)
+    flops = 2.0 * n ** 3
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local).start() if rank == 0 else None
     launches0 = lib.b200s_launch_count()
-    ms = timed(step, args.steps, sync, barrier)
+    t_region0 = time.time()
+    with ops.stage_timing(min(args.steps, 256)) as stages:
+        ms = timed(step, args.steps, sync, barrier)
+    t_region1 = time.time()
     launches = lib.b200s_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.window(t_region0, t_region1) if sampler else None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -316,7 +499,17 @@ def run_gpu_arm(args):
         raise SystemExit(f"device status {status}: a kernel gave up on a bounded wait")
     value = flops * args.steps / (ms * 1e-3) / 1e12
 
-    # ---- end to end through the reference-named API with host buffers ----
+    verify = None
+    if plan is not None:
+        verify = verify_sharded(plan, B, n, world, rank, dev, dist)
+        if not verify["bit_exact"] or verify["rel_fro_probe"] > 2e-2:
+            if rank == 0:
+                print(json.dumps({"error": "the row-sharded product failed its verification", "verify": verify}), flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+
+    # ---- end to end through the public API with host buffers ----
     hA = torch.empty(A.shape, dtype=A.dtype, pin_memory=True)
     hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True)
     hA.copy_(A)
@@ -336,11 +529,12 @@ def run_gpu_arm(args):
         def e2e_step():
             dA = hA.to(dev, non_blocking=True)
             dB = hB.to(dev, non_blocking=True)
-            if args.exchange.startswith("peer"):
-                out = plan(dA, dB)
-            else:
-                out = sharded_matmul(dA, dB, n, panels=args.panels, out=C, algo="classic", depth=depth, workspace=ws)
+            out = plan(dA, dB) if plan is not None else step_nccl(dA, dB)
             hC.copy_(out[r0:r1], non_blocking=True)
+
+        def step_nccl(dA, dB):
+            return sharded_matmul(dA, dB, n, panels=args.panels, out=C, algo=args.algo,
+                                  depth=-1 if args.algo == "auto" else depth, workspace=ws)
 
     e2e_steps = max(1, min(args.steps, 5))
     e2e_step()
@@ -350,66 +544,150 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = t.item()
     e2e_value = flops * e2e_steps / (ms_e2e * 1e-3) / 1e12
-    ms_dense = None
-    if world == 1:
-        # cuBLAS dense bf16 on the same GPU and inputs, same timing protocol as `value`
-        dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
-        for _ in range(max(args.warmup, 3)):
-            dense()
-        ms_dense = timed(dense, args.steps, sync, barrier) / args.steps
     h2d = (hA.numel() + hB.numel()) * 2
     d2h = hC.numel() * 2
+    del hA, hB, hC
 
     line = None
     if rank == 0:
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": "fixed_strassen_fp32_agg.strassen_matmul_n_layers" if world == 1
-                    else ("strassen_triton_b200.sharded.PeerShardedMatmul" if args.exchange != "nccl"
+                    else ("strassen_triton_b200.sharded.PeerShardedMatmul" if plan is not None
                           else "strassen_triton_b200.sharded.sharded_matmul")},
             "gpu_launches": int(launches),
         }
-        if world > 1:
-            line["config"]["exchange"] = args.exchange
-            line["config"]["panels"] = args.panels
-        if world == 1:
-            # per-kernel durations and the roofline of the dominant kernel (the grouped GEMM)
-            stages = stage_breakdown(ops, _lib, A, B, C, depth, args.steps)
-            t_gemm = stages["gemm_grouped"] * 1e-3
-            executed = (7.0 / 8.0) ** depth * flops
-            achieved = executed / t_gemm / 1e12
-            peak = peaks["bf16_sustained"]
-            line["roofline"] = {
-                "kernel": "gemm_kernel (grouped tcgen05 GEMM, 49 sub-products of 4096^3)", "bound": "tensor",
-                "achieved": round(achieved, 1), "peak": peak, "unit": UNIT, "frac": round(achieved / peak, 4),
-                "peak_kind": f"cuBLAS bf16 sustained, of {peaks['source']} (burst {peaks['bf16_burst']})",
-                "traffic": GEMM_DRAM_TRAFFIC_BYTES, "algorithmic_flops_per_launch": executed,
-                "duration_ms": round(stages["gemm_grouped"], 4)}
-            hbm = peaks["hbm_gbs"]
-            es = 2
-            blk = (n // 4) ** 2 * es
-            pre_bytes = n * n * es + 49 * blk
-            comb_bytes = 49 * blk + n * n * es
-            line["stages_ms"] = {k: round(v, 4) for k, v in stages.items()}
+    stage_names = ("operand_blocks_A", "operand_blocks_B", "products", "recombination")
+
+    if world > 1:
+        # per-rank stage times of rank 0's own block (library events during the timed steps); what is
+        # left of a step is the two device-side barriers and launch gaps
+        st = {k: round(stages[k], 4) for k in stage_names}
+        if rank == 0:
+            per_step = ms / args.steps
+            line["config"]["exchange"] = ("peer stores from the product kernel (no collective in the timed path)"
+                                          if args.exchange == "peer" else args.exchange)
+            line["config"]["panels"] = plan.panels if plan is not None else args.panels
+            if plan is not None:
+                line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
+                                              "shape": [plan.prow, n, n], "from": "tuner table" if args.algo == "auto" else "flag"}
+            calls = max(stages["calls"], 1) / args.steps     # panels per step
+            line["stages_ms"] = {"B_operand_blocks": round(st["operand_blocks_B"] * calls, 4),
+                                 "A_operand_blocks": round(st["operand_blocks_A"] * calls, 4),
+                                 "products": round(st["products"] * calls, 4),
+                                 "recombination_and_exchange": round(st["recombination"] * calls, 4)}
+            line["stages_ms"]["barriers_and_gaps"] = round(per_step - sum(line["stages_ms"].values()), 4)
+            line["stages_ms"]["note"] = ("rank 0; a dense block has one stage, the product kernel, whose epilogue also "
+                                         "performs the exchange")
+            line["verify"] = verify
+        if args.fsdp:
+            fs, twin_ok = fsdp_leg(world, rank, dev, dist)
+            if rank == 0:
+                line["fsdp_step"] = fs
+                line["fsdp_twin_ok"] = twin_ok
+    else:
+        # ---- comparison with cuBLAS dense on the same GPU, interleaved ----
+        dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
+        for _ in range(warmup):
+            dense()
+        inter = interleaved({"strassen": step, "cublas_dense": dense}, args.rounds, args.seconds, sampler, flops)
+        st, cu = inter["strassen"], inter["cublas_dense"]
+        line["interleaved"] = {
+            "protocol": f"{args.rounds} rounds of strassen, cublas_dense turns; a turn = 0.5 s rest, then back-to-back "
+                        f"calls for {args.seconds} s; burst = first 20 calls, sustained = last second",
+            "strassen": st, "cublas_dense": cu,
+            "ratio_burst": round(cu["burst_ms_median"] / st["burst_ms_median"], 4),
+            "ratio_sustained": round(cu["sustained_ms_median"] / st["sustained_ms_median"], 4)}
+        line["cublas_dense"] = {"value": cu["burst_tflops"], "sustained_value": cu["sustained_tflops"], "unit": UNIT,
+                                "ms_per_step": cu["burst_ms_median"],
+                                "protocol": "median over the interleaved turns (see `interleaved`)"}
+
+        # ---- the reference recursion on this GPU (oracle port on CUDA tensors, cuBLAS sub-products) ----
+        from oracle import strassen_oracle as so
+
+        ref_step = lambda: so.n_layers(A, B, depth, torch.bfloat16, True, False)  # noqa: E731
+        for _ in range(2):
+            ref_step()
+        ms_ref = timed(ref_step, 5, sync, barrier) / 5
+        line["reference_gpu"] = {"value": round(flops / (ms_ref * 1e-3) / 1e12, 2), "unit": UNIT,
+                                 "ms_per_step": round(ms_ref, 3),
+                                 "what": "the reference's torch recursion (fixed_strassen_fp32_agg.strassen_matmul_n_layers "
+                                         "as shipped, restated in oracle/) on CUDA tensors: cuBLAS sub-products and "
+                                         "eager elementwise passes, 5 steps"}
+        del ref_step
+        torch.cuda.empty_cache()
+
+        # ---- roofline of the dominant kernel, from the stage events of the timed steps ----
+        executed = (7.0 / 8.0) ** depth * flops
+        t_prod = stages["products"] * 1e-3
+        achieved = executed / t_prod / 1e12
+        region_s = ms * 1e-3
+        burst_region = region_s < 1.0
+        peak = peaks["bf16_burst"] if burst_region else peaks["bf16_sustained"]
+        prob = ops.make_problem(A, B, C, "classic", depth)[0]
+        fuse_used = resolved_schedule(lib, prob, fuse)
+        line["config"]["schedule"] = fuse_used
+        line["roofline"] = {
+            "kernel": "gemm_kernel (grouped tcgen05 GEMM over the 49 sub-products of 4096^3"
+                      + ("; fused form: its adder warps also form operand blocks and recombine C" if "fused" in fuse_used else "") + ")",
+            "bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": UNIT,
+            "frac": round(achieved / peak, 4),
+            "peak_kind": f"cuBLAS bf16 {'burst' if burst_region else 'sustained'} rate, of {peaks['source']} "
+                         f"(timed region {region_s:.2f} s)",
+            "traffic": round(GEMM_DRAM_BYTES_14_PRODUCTS * 49 / 14), "traffic_source": GEMM_DRAM_SOURCE,
+            "algorithmic_flops_per_launch": executed, "duration_ms": round(stages["products"], 4),
+            "duration_source": f"library stage events over the {stages['calls']} timed steps"}
+        hbm = peaks["hbm_gbs"]
+        blk = (n // 4) ** 2 * 2
+        line["stages_ms"] = {k: round(stages[k], 4) for k in stage_names}
+        line["stages_ms"]["sum"] = round(sum(stages[k] for k in stage_names), 4)
+        if "fused" not in fuse_used:
+            pre_bytes = n * n * 2 + 49 * blk
+            comb_bytes = 49 * blk + n * n * 2
             line["add_passes"] = {
-                "preadd_A_gbs": round(pre_bytes / (stages["preadd_A"] * 1e-3) / 1e9, 1),
-                "preadd_B_gbs": round(pre_bytes / (stages["preadd_B"] * 1e-3) / 1e9, 1),
-                "combine_gbs": round(comb_bytes / (stages["combine"] * 1e-3) / 1e9, 1),
+                "preadd_A_gbs": round(pre_bytes / (stages["operand_blocks_A"] * 1e-3) / 1e9, 1),
+                "preadd_B_gbs": round(pre_bytes / (stages["operand_blocks_B"] * 1e-3) / 1e9, 1),
+                "combine_gbs": round(comb_bytes / (stages["recombination"] * 1e-3) / 1e9, 1),
                 "hbm_peak_gbs": hbm, "peak_kind": f"copy bandwidth, of {peaks['source']}"}
-            line["cublas_dense"] = {"value": round(flops / (ms_dense * 1e-3) / 1e12, 2), "unit": UNIT,
-                                    "ms_per_step": round(ms_dense, 4),
-                                    "protocol": "same steps and warm-up as `value`, started after the PCIe-bound "
-                                                "end-to-end phase so that both start on an equally rested GPU"}
-            line["cpu_baseline"] = cpu_baseline()
+
+        # ---- one GPU on the multi-GPU workload: the basis of T(1) / (P T(P)) ----
+        del A, B, C, ws
+        torch.cuda.empty_cache()
+        n2 = 32768
+        A2, B2 = seeded_inputs(n2, n2, "normal", 0, dev)
+        C2 = torch.empty((n2, n2), dtype=torch.bfloat16, device=dev)
+        p2, _, _ = ops.make_problem(A2, B2, C2, "auto", -1)
+        ws2 = torch.empty(max(ops.workspace_bytes(p2), 1), dtype=torch.uint8, device=dev)
+        big = lambda: ops.matmul_out(A2, B2, C2, algo="auto", depth=-1, workspace=ws2)  # noqa: E731
+        for _ in range(3):
+            big()
+        line["t1_32768_ms"] = round(timed(big, 5, sync, barrier) / 5, 3)
+        a32, d32 = ops.resolve(p2)
+        line["t1_32768_algo"] = {"algo": {1: "dense", 2: "classic", 3: "winograd"}[a32], "depth": d32}
+        del A2, B2, C2, ws2
+        torch.cuda.empty_cache()
+        line["cpu_baseline"] = cpu_baseline()
+    if sampler:
+        sampler.stop()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+
+
+def resolved_schedule(lib, prob, fuse=0):
+    """Name of the schedule the library runs for this problem (fuse 0: the one it picks itself)."""
+    a, d, f = ctypes.c_int32(0), ctypes.c_int32(0), ctypes.c_int32(0)
+    lib.b200s_tuner_lookup_schedule(prob.M, prob.N, prob.K, prob.in_dtype, ctypes.byref(a), ctypes.byref(d), ctypes.byref(f))
+    if fuse == 0:
+        fuse = f.value if f.value else 2
+    return {1: "fused (one persistent kernel)", 2: "separate passes (pre-add A, pre-add B, grouped GEMM, recombination)",
+            3: "fused kernel, last quadrant of C recombined by a full-width launch after it"}[fuse]
 
 
 def main():
@@ -418,16 +696,30 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--panels", type=int, default=1, help="row panels per rank for exchange/compute overlap (N > 1)")
+    ap.add_argument("--rounds", type=int, default=5, help="N = 1: rounds of the interleaved comparison with cuBLAS")
+    ap.add_argument("--seconds", type=float, default=2.0, help="N = 1: length of one turn of an arm")
+    ap.add_argument("--schedule", default="auto", choices=["auto", "separate", "fused", "fused_all"],
+                    help="N = 1: schedule of the Strassen passes ('auto' = the library's tuner table)")
+    ap.add_argument("--panels", type=int, default=1, help="row panels per rank (N > 1)")
+    ap.add_argument("--algo", default="auto", choices=["auto", "dense", "classic", "winograd"],
+                    help="N > 1: per-rank algorithm ('auto' = the library's tuner table)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "peer_push", "peer_copy", "nccl"],
-                    help="N > 1: 'peer' = recombination kernel stores into every rank's C over NVLink; "
+                    help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink; "
                          "'nccl' = all-gather of the row blocks")
+    ap.add_argument("--fsdp", type=int, default=1, help="N > 1: also time the FSDP GPT-2 step (0 = skip)")
+    ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, dense, preadd, "
+                                                 "combine, fused")
+    ap.add_argument("--n", type=int, default=4096, help="--only: matrix extent")
+    ap.add_argument("--products", type=int, default=14, help="--only gemm_grouped: products in the batch")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU path exists for the b200 arm)")
+    if args.only:
+        run_only(args)
+        return
     run_gpu_arm(args)
 
 

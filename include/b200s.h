@@ -184,10 +184,11 @@ int b200s_static_status(void* stream, int32_t* status_out, int32_t* detail_out);
 int b200s_resolve(const b200s_problem* p, int32_t* algo_out, int32_t* depth_out);
 
 /*
- * Tuner table: measured (M,N,K,in_dtype) -> (algo, depth) entries; lookups pick the entry whose
- * log-volume is nearest and fall back to a dense product below the smallest recorded crossover.
- * The table is process-wide, guarded by a mutex. File format: one entry per line,
- * "M N K in_dtype algo depth".
+ * Tuner table: measured (M,N,K,in_dtype) -> (algo, depth, schedule) entries; lookups pick the entry
+ * nearest in log-extents and fall back to a dense product below the smallest recorded crossover.
+ * The schedule is a b200s_problem.fuse value (0 = none recorded: the built-in rule applies) and is
+ * used when the caller leaves `fuse` and `pipeline` at 0. The table is process-wide, guarded by a
+ * mutex. File format: one entry per line, "M N K in_dtype algo depth [fuse]".
  */
 int b200s_tuner_clear(void);
 int b200s_tuner_record(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t algo, int32_t depth);
@@ -195,6 +196,10 @@ int b200s_tuner_load(const char* path);
 int b200s_tuner_save(const char* path);
 int b200s_tuner_lookup(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t* algo_out,
                        int32_t* depth_out);
+int b200s_tuner_record_schedule(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t algo, int32_t depth,
+                                int32_t fuse);
+int b200s_tuner_lookup_schedule(int64_t M, int64_t N, int64_t K, int32_t in_dtype, int32_t* algo_out,
+                                int32_t* depth_out, int32_t* fuse_out);
 
 /*
  * Reads (device -> host, synchronising `stream`) and clears the per-device status word that

@@ -78,6 +78,10 @@ SIGNATURES = {
     "b200s_tuner_save": (ctypes.c_int, [ctypes.c_char_p]),
     "b200s_tuner_lookup": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
                                           _P(ctypes.c_int32), _P(ctypes.c_int32)]),
+    "b200s_tuner_record_schedule": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                                                   ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
+    "b200s_tuner_lookup_schedule": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+                                                   _P(ctypes.c_int32), _P(ctypes.c_int32), _P(ctypes.c_int32)]),
     "b200s_device_status": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int32), _P(ctypes.c_int32)]),
     "b200s_wait_probe": (ctypes.c_int, [ctypes.c_uint64, ctypes.c_void_p]),
     "b200s_static_status": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_int32), _P(ctypes.c_int32)]),

@@ -48,7 +48,6 @@ struct GemmKernelParams {
   int32_t fmt;                // operand format field of the instruction descriptor
   int32_t out_dtype, beta;
   int32_t tma_store;          // 1: the epilogue stages tiles in shared memory and stores them with TMA
-  int32_t l2_a, l2_b;         // L2 policy of the operand loads (ptx::make_l2_policy kinds)
   int32_t n_dst;              // copies of C the TMA-store epilogue writes (1 unless the product is exchanged)
   int64_t ldc, strideC;
   void* C;
@@ -369,15 +368,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
-      const uint64_t policy_a = ptx::make_l2_policy(p.l2_a), policy_b = ptx::make_l2_policy(p.l2_b);
       [[maybe_unused]] int group_ready = 0;
       if constexpr (F::kOn) group_ready = fz.groups_formed;
 #ifdef B200S_FUSED_TRACE
       const uint64_t trace_p0 = ptx::global_timer_ns();
 #endif
-      for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters) {
+      int it = 0;
+      for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters, ++it) {
         int b, mt, nt;
         decode_tile(p, tile, b, mt, nt);
+        // Every other tile of a cluster walks K backwards: it then starts with the K slices its
+        // neighbours in the previous wave touched last, which are the ones still in L2 (walking
+        // forwards every time is the cyclic pattern an LRU cache serves worst).
+        const bool k_reversed = (it & 1) != 0;
         if constexpr (F::kOn) {
           // first tile of a new outer group: every CTA's adders must have stored its operand blocks
           const int g = b / fz.np2;
@@ -408,17 +411,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           const uint32_t sA = base + stage * STAGE_BYTES;
           const uint32_t sB = sA + A_BYTES;
-          const int k0 = kb * BKE;
+          const int k0 = (k_reversed ? p.k_blocks - 1 - kb : kb) * BKE;
           // With a CTA pair both CTAs' bytes are counted on the leader's barrier.
           uint32_t fb = full_bar(stage);
           if constexpr (kCtaGroup == 2) fb = ptx::mapa_cluster(fb, 0);
           if (cta_rank == 0) ptx::mbar_expect_tx(full_bar(stage), kCtaGroup * STAGE_BYTES);
           auto load = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
-            const uint64_t policy = m == &tmA ? policy_a : policy_b;
             if constexpr (kCtaGroup == 2)
-              ptx::tma_load_3d_pair_hint(dst, m, fb, c0, c1, b, policy);
+              ptx::tma_load_3d_pair(dst, m, fb, c0, c1, b);
             else
-              ptx::tma_load_3d_hint(dst, m, fb, c0, c1, b, policy);
+              ptx::tma_load_3d(dst, m, fb, c0, c1, b);
           };
           if (!p.a_mn) {
             load(sA, &tmA, k0, m0);
@@ -721,10 +723,7 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int dtype, int64_t rows,
 }
 
 // m-tiles that share a band of n-tiles in the tile order (L2 reuse of the B tiles of a band).
-#ifndef B200S_RASTER_GROUP
-#define B200S_RASTER_GROUP 8
-#endif
-constexpr int kRasterGroup = B200S_RASTER_GROUP;
+constexpr int kRasterGroup = 8;
 
 template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, GemmKernelParams kp,
@@ -870,18 +869,6 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   if (total > INT32_MAX) return B200S_ERR_BAD_SHAPE;
   kp.total_tiles = static_cast<int32_t>(total);
   kp.raster_group = kRasterGroup;
-  // A grouped launch walks one product after the other, m-band by m-band: the B block of the current
-  // product is read again by every band (and by the next wave of tiles), its A rows only while their
-  // band runs. When a B block fits in L2 with room to spare it is asked to stay (evict last) and the
-  // A rows to leave first; a single large product keeps the default policy.
-  const double b_block_bytes = static_cast<double>(g.N) * static_cast<double>(g.K) * static_cast<double>(es);
-#ifdef B200S_NO_L2_HINTS
-  const bool keep_b = false;
-#else
-  const bool keep_b = g.batch > 1 && b_block_bytes <= 48.0 * 1024 * 1024;
-#endif
-  kp.l2_a = keep_b ? 1 : 0;
-  kp.l2_b = keep_b ? 2 : 0;
   kp.a_mn = g.a_major == B200S_MN_MAJOR;
   kp.b_mn = g.b_major == B200S_MN_MAJOR;
   kp.fmt = tf32 ? 2 : (g.in_dtype == B200S_BF16 ? 1 : 0);

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import functools
+import math
 import os
 import time
 
@@ -35,10 +36,17 @@ VOCAB = 50257
 VOCAB_PADDED = 50304
 
 
+def _linear_factory(depth, device, plain: bool):
+    """LinearStrassen (the library's kernels), or nn.Linear for the twin model of the check."""
+    if plain:
+        return functools.partial(nn.Linear, bias=False, device=device)
+    return functools.partial(LinearStrassen, bias=False, depth=depth, device=device)
+
+
 class Block(nn.Module):
-    def __init__(self, d: int, heads: int, depth, device):
+    def __init__(self, d: int, heads: int, depth, device, plain: bool = False):
         super().__init__()
-        mk = functools.partial(LinearStrassen, bias=False, depth=depth, device=device)
+        mk = _linear_factory(depth, device, plain)
         self.heads = heads
         self.ln1 = nn.LayerNorm(d, device=device)
         self.ln2 = nn.LayerNorm(d, device=device)
@@ -56,13 +64,13 @@ class Block(nn.Module):
 
 
 class GPT(nn.Module):
-    def __init__(self, layers=12, d=768, heads=12, seq=1024, depth=None, device="cuda"):
+    def __init__(self, layers=12, d=768, heads=12, seq=1024, depth=None, device="cuda", plain: bool = False):
         super().__init__()
         self.wte = nn.Embedding(VOCAB_PADDED, d, device=device)
         self.wpe = nn.Embedding(seq, d, device=device)
-        self.blocks = nn.ModuleList(Block(d, heads, depth, device) for _ in range(layers))
+        self.blocks = nn.ModuleList(Block(d, heads, depth, device, plain) for _ in range(layers))
         self.ln_f = nn.LayerNorm(d, device=device)
-        self.lm_head = LinearStrassen(d, VOCAB_PADDED, bias=False, depth=depth, device=device)
+        self.lm_head = _linear_factory(depth, device, plain)(d, VOCAB_PADDED)
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.Embedding)):
                 nn.init.normal_(m.weight, std=0.02)
@@ -76,8 +84,10 @@ class GPT(nn.Module):
         return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
 
 
-def build(layers, seq, depth, device, world):
-    model = GPT(layers=layers, seq=seq, depth=depth, device=device)
+def build(layers, seq, depth, device, world, plain: bool = False, state=None):
+    model = GPT(layers=layers, seq=seq, depth=depth, device=device, plain=plain)
+    if state is not None:
+        model.load_state_dict(state)
     if world == 0:
         return model.to(torch.bfloat16)
     mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16, buffer_dtype=torch.bfloat16)
@@ -99,6 +109,44 @@ def train_steps(model, steps, batch, seq, rank, lr=3e-4):
         opt.zero_grad(set_to_none=True)
         losses.append(loss.item())
     return losses
+
+
+def twin_check(world, rank, layers=2, seq=256, batch=4):
+    """The FSDP smoke check: a `layers`-layer model whose Linears are LinearStrassen and a twin with
+    nn.Linear holding the same weights take one forward/backward on the same tokens under the same
+    FSDP wrapping; their losses and every local gradient shard must agree within the tolerance of a
+    bf16 product computed by two different kernels. Returns (ok, details)."""
+    torch.manual_seed(1234)
+    base = GPT(layers=layers, seq=seq, depth=None, device="cuda")
+    state = {k: v.clone() for k, v in base.state_dict().items()}
+    del base
+    ours = build(layers, seq, None, "cuda", world, plain=False, state=state)
+    twin = build(layers, seq, None, "cuda", world, plain=True, state=state)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    ids = torch.randint(0, VOCAB, (batch, seq + 1), generator=g, device="cuda")
+    losses, grads = [], []
+    for model in (ours, twin):
+        loss = model(ids[:, :-1], ids[:, 1:])
+        loss.backward()
+        losses.append(loss.item())
+        grads.append({n: p.grad.detach().float().clone() for n, p in model.named_parameters()
+                      if p.grad is not None and p.grad.numel() > 0})
+    worst, worst_name = 0.0, ""
+    for name, g_ours in grads[0].items():
+        g_twin = grads[1].get(name)
+        if g_twin is None or g_twin.shape != g_ours.shape:
+            return False, {"error": f"gradient shard of {name} has no twin"}
+        denom = g_twin.norm().item()
+        if denom == 0.0:
+            continue
+        rel = ((g_ours - g_twin).norm().item()) / denom
+        if rel > worst:
+            worst, worst_name = rel, name
+    dloss = abs(losses[0] - losses[1])
+    ok = bool(worst < 3e-2 and dloss < 2e-2 and len(grads[0]) > 0 and all(math.isfinite(x) for x in losses))
+    return ok, {"layers": layers, "loss_ours": round(losses[0], 4), "loss_twin": round(losses[1], 4),
+                "worst_grad_rel_fro": round(worst, 5), "worst_param": worst_name, "grad_shards_compared": len(grads[0]),
+                "tolerance": "loss 2e-2, gradients 3e-2 relative Frobenius (bf16 products from two kernels)"}
 
 
 def main():
