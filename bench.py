@@ -469,7 +469,8 @@ def run_gpu_arm(args):
 
             plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
                                      panels=args.panels, device=dev,
-                                     exchange={"peer": "store", "peer_push": "push", "peer_copy": "copy"}[args.exchange])
+                                     exchange={"peer": "auto", "peer_store": "store", "peer_multicast": "multicast",
+                                               "peer_push": "push", "peer_copy": "copy"}[args.exchange])
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
         else:
@@ -569,8 +570,9 @@ def run_gpu_arm(args):
         st = {k: round(stages[k], 4) for k in stage_names}
         if rank == 0:
             per_step = ms / args.steps
-            line["config"]["exchange"] = ("peer stores from the product kernel (no collective in the timed path)"
-                                          if args.exchange == "peer" else args.exchange)
+            line["config"]["exchange"] = (f"{plan.exchange}: stores from the product kernel into every rank's C (no "
+                                          "collective in the timed path)" if plan is not None and plan.exchange in
+                                          ("store", "multicast") else args.exchange)
             line["config"]["panels"] = plan.panels if plan is not None else args.panels
             if plan is not None:
                 line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
@@ -703,9 +705,10 @@ def main():
     ap.add_argument("--panels", type=int, default=1, help="row panels per rank (N > 1)")
     ap.add_argument("--algo", default="auto", choices=["auto", "dense", "classic", "winograd"],
                     help="N > 1: per-rank algorithm ('auto' = the library's tuner table)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_push", "peer_copy", "nccl"],
-                    help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink; "
-                         "'nccl' = all-gather of the row blocks")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_push", "peer_copy", "nccl"],
+                    help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink (NVLS multicast "
+                         "stores for dense blocks where available, plain peer stores otherwise); 'nccl' = all-gather of "
+                         "the row blocks")
     ap.add_argument("--fsdp", type=int, default=1, help="N > 1: also time the FSDP GPT-2 step (0 = skip)")
     ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, dense, preadd, "
                                                  "combine, fused")

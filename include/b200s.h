@@ -260,14 +260,27 @@ int b200s_combine_peers(const b200s_problem* p, const void* products_device, voi
  * b200s_matmul whose result goes to n_dst (1..8) destinations at once: C_list[i] is the device address
  * of element (0,0) of the product inside destination i, all with leading dimension p->ldc; beta must
  * be 0 and batch 1. A dense product stores every finished tile to all destinations from the GEMM's
- * TMA-store epilogue (so the exchange of a row-sharded product rides on the product kernel, tile by
- * tile, and needs C rows that are multiples of 16 bytes); a one- or two-level Strassen product runs its
- * sequential schedule and ends in b200s_combine_peers. Destinations may be other GPUs' memory mapped
+ * epilogue: C_list[0] (put this GPU's own copy there) by TMA, the others by ordinary 16-byte stores
+ * of the same staged tile, so the exchange of a row-sharded product rides on the product kernel, tile
+ * by tile (it needs C rows that are multiples of 16 bytes); a one- or two-level Strassen product runs
+ * its sequential schedule and ends in b200s_combine_peers. Destinations may be other GPUs' memory mapped
  * into this process; only stores go there, every load reads this GPU's memory. The reference has no
  * multi-GPU product: this is the per-rank step of the row-sharded one.
  */
 int b200s_matmul_peers(const b200s_problem* p, const void* A_device, const void* B_device, void* const* C_list,
                        int n_dst, void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
+ * The dense row-sharded step with the exchange done by the NVSwitch: C_local is this GPU's copy of
+ * the rows (written by TMA as in b200s_matmul), C_multicast the NVLS multicast address of the same
+ * rows (an address bound to every GPU's copy of C, e.g. the multicast pointer of a symmetric-memory
+ * allocation). Every finished tile is stored once more with multimem.st to C_multicast and the
+ * switch replicates it into all GPUs' memory: each GPU sends its rows once instead of once per peer.
+ * Dense products only (B200S_ERR_BAD_ALGO otherwise), beta 0, batch 1, rows of C multiples of 16
+ * bytes. No counterpart in the reference.
+ */
+int b200s_matmul_multicast(const b200s_problem* p, const void* A_device, const void* B_device, void* C_local,
+                           void* C_multicast, void* workspace_device, size_t workspace_bytes, void* stream);
 
 /*
  * Barrier number `epoch` among `world` (1..8) GPUs on `stream`: pads[r] is rank r's pad of at least

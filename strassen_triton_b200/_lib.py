@@ -93,6 +93,8 @@ SIGNATURES = {
                                            ctypes.c_void_p]),
     "b200s_matmul_peers": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int,
                                           ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "b200s_matmul_multicast": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "b200s_peer_barrier": (ctypes.c_int, [_P(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_uint32,
                                           ctypes.c_uint64, ctypes.c_void_p]),
     "b200s_push_rows": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,

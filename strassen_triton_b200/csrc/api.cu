@@ -684,7 +684,7 @@ int b200s_push_rows(const void* src, void* const* dst_list, int n_dst, size_t by
 
 // C (+)= A . B into C, or (n_dst > 0, beta 0, one product) into every destination of dst_list.
 static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* const* dst_list,
-                      int n_dst, void* workspace, size_t workspace_bytes, void* stream_v) {
+                      int n_dst, void* workspace, size_t workspace_bytes, void* stream_v, void* mc_dst = nullptr) {
   if (!p_in || !A || !B || (!C && n_dst == 0)) return B200S_ERR_NULL_POINTER;
   Plan plan;
   int rc = make_plan(p_in, &plan);
@@ -735,7 +735,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   uint8_t* B3 = A3 + plan.a3_bytes;
   if (plan.depth == 0) {
     g.A = A, g.B = B, g.C = C;
-    g.n_dst = n_dst, g.C_list = dst_list;
+    g.n_dst = n_dst, g.C_list = dst_list, g.mc_dst = mc_dst;
     g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
     g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
     g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
@@ -763,8 +763,6 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   void* Mp = ws + plan.sa_bytes + plan.sb_bytes;
 
   const double volume = static_cast<double>(p->M) * static_cast<double>(p->N) * static_cast<double>(p->K);
-  // The fused schedule: asked for (fuse 1 / 3), or the library's choice (fuse 0) for products from
-  // kFusedFrom^3 on when the caller left the schedule open.
   int fuse = p->fuse;
   if (fuse == 0 && p->pipeline == 0) {
     // The caller left the schedule open: the tuner table's entry for this shape, else separate passes.
@@ -841,6 +839,17 @@ int b200s_matmul_peers(const b200s_problem* p, const void* A, const void* B, voi
   for (int d = 0; d < n_dst; ++d)
     if (!C_list[d]) return B200S_ERR_NULL_POINTER;
   return run_matmul(p, A, B, nullptr, C_list, n_dst, workspace, workspace_bytes, stream);
+}
+
+int b200s_matmul_multicast(const b200s_problem* p, const void* A, const void* B, void* C_local, void* C_multicast,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p || !C_local || !C_multicast) return B200S_ERR_NULL_POINTER;
+  if (p->batch != 1 || p->beta != 0) return B200S_ERR_BAD_SHAPE;
+  int32_t algo = 0, depth = 0;
+  int rc = b200s_resolve(p, &algo, &depth);
+  if (rc) return rc;
+  if (depth != 0) return B200S_ERR_BAD_ALGO;  // the multicast store lives in the dense product's epilogue
+  return run_matmul(p, A, B, C_local, nullptr, 0, workspace, workspace_bytes, stream, C_multicast);
 }
 
 int b200s_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, uint64_t limit_ns, void* stream) {

@@ -49,6 +49,9 @@ struct GemmArgs {
   // TMA-store epilogue: beta 0, 16-byte aligned rows). Destinations may be peer GPUs' memory.
   int n_dst = 0;
   void* const* C_list = nullptr;
+  // Optional: an NVLS multicast address of C(0,0) that maps to every GPU's copy. C (or C_list[0])
+  // is then this GPU's own copy, written by TMA, and every tile is also stored once to mc_dst.
+  void* mc_dst = nullptr;
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 // One-thread kernel that waits `limit_ns` on a barrier nobody signals and reports the give-up in the

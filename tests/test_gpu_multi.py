@@ -2,6 +2,7 @@
 every exchange variant, the whole C of every rank compared bit for bit with locally computed panel
 products. Plain peer stores and NCCL only; NVLS is switched off for the child processes."""
 import os
+import re
 import socket
 import subprocess
 import sys
@@ -31,6 +32,7 @@ def test_peer_sharded_product_on_several_gpus(built_library, world):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "peer_sharded_worker.py")]
     out = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
-    lines = [ln for ln in out.stdout.splitlines() if ln.startswith(("ok ", "FAILED "))]
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert sorted(lines) == [f"ok {r}" for r in range(world)], out.stdout[-3000:]
+    assert "FAILED" not in out.stdout, out.stdout[-3000:]
+    # the ranks print at the same moment: their lines may run into one another
+    assert sorted(int(r) for r in re.findall(r"ok (\d+)", out.stdout)) == list(range(world)), out.stdout[-3000:]

@@ -46,7 +46,7 @@ def test_peer_sharded_plan_single_rank(single_rank_group, exchange, algo, depth,
                                  panels=panels, exchange=exchange, barrier_ms=200)
     except RuntimeError as e:  # symmetric memory not available in this environment
         pytest.skip(f"symmetric memory rendezvous unavailable: {e}")
-    assert (plan.algo, plan.depth, plan.panels) == (algo, depth, panels)
+    assert (plan.algo, plan.depth, plan.panels, plan.exchange) == (algo, depth, panels, exchange)
     for _ in range(2):
         C = plan(A, B)
     plan.check()
