@@ -596,14 +596,24 @@ def run_gpu_arm(args):
         dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
         for _ in range(warmup):
             dense()
-        inter = interleaved({"strassen": step, "cublas_dense": dense}, args.rounds, args.seconds, sampler, flops)
-        st, cu = inter["strassen"], inter["cublas_dense"]
+        prob = ops.make_problem(A, B, C, "classic", depth)[0]
+        fuse_used = resolved_schedule(lib, prob, fuse)
+        sep = lambda: ops.matmul_out(A, B, C, algo="classic", depth=depth, fuse=2, pipeline=2, workspace=ws)  # noqa: E731
+        fus = lambda: ops.matmul_out(A, B, C, algo="classic", depth=depth, fuse=3, workspace=ws)  # noqa: E731
+        inter = interleaved({"strassen_separate": sep, "strassen_fused": fus, "cublas_dense": dense}, args.rounds,
+                            args.seconds, sampler, flops)
+        mine = "strassen_fused" if "fused" in fuse_used else "strassen_separate"
+        st, cu = inter[mine], inter["cublas_dense"]
         line["interleaved"] = {
-            "protocol": f"{args.rounds} rounds of strassen, cublas_dense turns; a turn = 0.5 s rest, then back-to-back "
-                        f"calls for {args.seconds} s; burst = first 20 calls, sustained = last second",
-            "strassen": st, "cublas_dense": cu,
+            "protocol": f"{args.rounds} rounds of strassen_separate, strassen_fused, cublas_dense turns; a turn = 0.5 s rest, "
+                        f"then back-to-back calls for {args.seconds} s; burst = first 20 calls, sustained = last second; "
+                        "the SM clock is the median of the samples taken during the turn",
+            "library_default": mine, **inter,
             "ratio_burst": round(cu["burst_ms_median"] / st["burst_ms_median"], 4),
-            "ratio_sustained": round(cu["sustained_ms_median"] / st["sustained_ms_median"], 4)}
+            "ratio_sustained": round(cu["sustained_ms_median"] / st["sustained_ms_median"], 4),
+            "ratios_by_schedule": {k: {"burst": round(cu["burst_ms_median"] / inter[k]["burst_ms_median"], 4),
+                                       "sustained": round(cu["sustained_ms_median"] / inter[k]["sustained_ms_median"], 4)}
+                                   for k in ("strassen_separate", "strassen_fused")}}
         line["cublas_dense"] = {"value": cu["burst_tflops"], "sustained_value": cu["sustained_tflops"], "unit": UNIT,
                                 "ms_per_step": cu["burst_ms_median"],
                                 "protocol": "median over the interleaved turns (see `interleaved`)"}
@@ -630,8 +640,6 @@ def run_gpu_arm(args):
         region_s = ms * 1e-3
         burst_region = region_s < 1.0
         peak = peaks["bf16_burst"] if burst_region else peaks["bf16_sustained"]
-        prob = ops.make_problem(A, B, C, "classic", depth)[0]
-        fuse_used = resolved_schedule(lib, prob, fuse)
         line["config"]["schedule"] = fuse_used
         line["roofline"] = {
             "kernel": "gemm_kernel (grouped tcgen05 GEMM over the 49 sub-products of 4096^3"

@@ -143,6 +143,16 @@ int b200s_matmul(const b200s_problem* p, const void* A_device, const void* B_dev
                  void* workspace_device, size_t workspace_bytes, void* stream);
 
 /*
+ * C (+)= A . B + bias: b200s_matmul with a row vector of N elements of out_dtype added to every row
+ * of the product in fp32, before the one rounding to out_dtype - the `x @ W.T + b` of the reference's
+ * LinearStrassen (model/layers.py:271-272) without a separate pass over the output. A dense product
+ * adds it in the GEMM epilogue, a one- or two-level Strassen product in its recombination kernel
+ * (the sequential schedule is used; more than two levels return B200S_ERR_BAD_DEPTH).
+ */
+int b200s_matmul_bias(const b200s_problem* p, const void* A_device, const void* B_device, const void* bias_device,
+                      void* C_device, void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
  * C (+)= A . B like b200s_matmul, for callers that cannot hand over scratch memory. (No counterpart
  * in the reference: it is an addition of this library.)
  *
@@ -225,8 +235,9 @@ int b200s_wait_probe(uint64_t limit_ns, void* stream);
  * calls, writes the mean duration in milliseconds of the four stages to stage_ms_out[0..3] - operand
  * blocks of A, operand blocks of B, products, recombination; in the fused schedule: blocks of A of the
  * first group, blocks of B of the first group, the fused kernel, the recombination left after it -
- * and the number of calls measured to *calls_out. Other schedules (pipelined, more than two levels,
- * dense) record nothing. One collection at a time, process-wide.
+ * and the number of calls measured to *calls_out. A dense product counts entirely as "products";
+ * the multi-stream pipelined schedule and products of more than two levels record nothing. One
+ * collection at a time, process-wide.
  */
 int b200s_profile_begin(int max_calls);
 int b200s_profile_end(float* stage_ms_out, int32_t* calls_out);

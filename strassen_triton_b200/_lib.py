@@ -68,6 +68,8 @@ SIGNATURES = {
     "b200s_workspace_bytes": (ctypes.c_int, [_P(Problem), _P(ctypes.c_size_t)]),
     "b200s_matmul": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                     ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "b200s_matmul_bias": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                         ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "b200s_matmul_static": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_void_p]),
     "b200s_resolve": (ctypes.c_int, [_P(Problem), _P(ctypes.c_int32), _P(ctypes.c_int32)]),

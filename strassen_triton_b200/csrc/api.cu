@@ -638,7 +638,13 @@ int b200s_preadd(const b200s_problem* p, int side, const void* X, void* out, voi
   return launch_preadd(a, static_cast<cudaStream_t>(stream));
 }
 
+static int combine_with_bias(const b200s_problem* p, const void* products, void* C, const void* bias, void* stream);
+
 int b200s_combine(const b200s_problem* p, const void* products, void* C, void* stream) {
+  return combine_with_bias(p, products, C, nullptr, stream);
+}
+
+static int combine_with_bias(const b200s_problem* p, const void* products, void* C, const void* bias, void* stream) {
   if (!p || !products || !C) return B200S_ERR_NULL_POINTER;
   Plan plan;
   int rc = make_plan(p, &plan);
@@ -657,6 +663,7 @@ int b200s_combine(const b200s_problem* p, const void* products, void* C, void* s
   c.prod_dtype = plan.prod_dtype;
   c.out_dtype = p->out_dtype;
   c.beta = p->beta;
+  c.bias = bias;
   if (!device_status_words()) return B200S_ERR_NO_DEVICE;
   return launch_combine(c, static_cast<cudaStream_t>(stream));
 }
@@ -684,7 +691,8 @@ int b200s_push_rows(const void* src, void* const* dst_list, int n_dst, size_t by
 
 // C (+)= A . B into C, or (n_dst > 0, beta 0, one product) into every destination of dst_list.
 static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, void* C, void* const* dst_list,
-                      int n_dst, void* workspace, size_t workspace_bytes, void* stream_v, void* mc_dst = nullptr) {
+                      int n_dst, void* workspace, size_t workspace_bytes, void* stream_v, void* mc_dst = nullptr,
+                      const void* bias = nullptr) {
   if (!p_in || !A || !B || (!C && n_dst == 0)) return B200S_ERR_NULL_POINTER;
   Plan plan;
   int rc = make_plan(p_in, &plan);
@@ -721,7 +729,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   }
 
   if (plan.depth > 2) {
-    if (n_dst > 0) return B200S_ERR_BAD_DEPTH;  // several destinations: dense, or one pipeline of up to two levels
+    if (n_dst > 0 || bias) return B200S_ERR_BAD_DEPTH;  // several destinations or a bias: dense, or one pipeline of up to two levels
     return run_deep(p, plan, A, B, C, ws + plan.ta_bytes + plan.tb_bytes, stream);
   }
 
@@ -735,7 +743,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   uint8_t* B3 = A3 + plan.a3_bytes;
   if (plan.depth == 0) {
     g.A = A, g.B = B, g.C = C;
-    g.n_dst = n_dst, g.C_list = dst_list, g.mc_dst = mc_dst;
+    g.n_dst = n_dst, g.C_list = dst_list, g.mc_dst = mc_dst, g.bias = bias;
     g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
     g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
     g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;
@@ -770,7 +778,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
     // product and costs more energy than it hides time, so it is nobody's default.)
     fuse = plan.table_fuse != 0 ? plan.table_fuse : 2;
   }
-  if (n_dst == 0 && (fuse == 1 || fuse == 3)) {
+  if (n_dst == 0 && !bias && (fuse == 1 || fuse == 3)) {
     if (fused_eligible(p, plan)) {
       uint32_t* flags = reinterpret_cast<uint32_t*>(ws + plan.total_bytes - plan.flag_bytes);
       return run_fused(p, plan, A, B, C, Sa, Sb, Mp, flags, fuse == 3, stream);
@@ -779,7 +787,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   }
   // Large single products run the pipelined driver unless the caller chose otherwise.
   const bool pipelined = p->pipeline == 1 || (p->pipeline == 0 && volume >= 24576.0 * 24576.0 * 24576.0);
-  if (n_dst == 0 && p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
+  if (n_dst == 0 && !bias && p->batch == 1 && pipelined && !plan.split3) return run_pipelined(p, plan, A, B, C, Sa, Sb, Mp, stream);
 
   const int prof = prof_new_call();
   prof_mark(prof, 0, stream);
@@ -821,7 +829,8 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   if (rc) return rc;
   prof_mark(prof, 3, stream);
 
-  rc = n_dst > 0 ? b200s_combine_peers(p, Mp, dst_list, n_dst, stream_v) : b200s_combine(p, Mp, C, stream_v);
+  if (n_dst > 0 && bias) return B200S_ERR_BAD_SHAPE;  // the multi-destination recombination carries no bias
+  rc = n_dst > 0 ? b200s_combine_peers(p, Mp, dst_list, n_dst, stream_v) : combine_with_bias(p, Mp, C, bias, stream_v);
   prof_mark(prof, 4, stream);
   return rc;
 }
@@ -830,6 +839,13 @@ int b200s_matmul(const b200s_problem* p, const void* A, const void* B, void* C, 
                  size_t workspace_bytes, void* stream) {
   if (!C) return B200S_ERR_NULL_POINTER;
   return run_matmul(p, A, B, C, nullptr, 0, workspace, workspace_bytes, stream);
+}
+
+int b200s_matmul_bias(const b200s_problem* p, const void* A, const void* B, const void* bias, void* C, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  if (!C || !bias) return B200S_ERR_NULL_POINTER;
+  if (p && p->out_dtype != B200S_FP32 && (reinterpret_cast<uintptr_t>(bias) & 1u)) return B200S_ERR_BAD_ALIGNMENT;
+  return run_matmul(p, A, B, C, nullptr, 0, workspace, workspace_bytes, stream, nullptr, bias);
 }
 
 int b200s_matmul_peers(const b200s_problem* p, const void* A, const void* B, void* const* C_list, int n_dst,

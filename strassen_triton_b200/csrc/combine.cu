@@ -31,7 +31,14 @@ struct CombineKernelParams {
   int64_t Mb, nb_vec;  // block rows, 16-byte product vectors per block row
   int64_t ldc, strideC;
   int32_t out_dtype, beta, vec_ok;
+  const void* bias;
 };
+
+__device__ __forceinline__ float bias_at(const void* bias, int out_dtype, int64_t col) {
+  if (out_dtype == B200S_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + col));
+  if (out_dtype == B200S_FP16) return __half2float(__ldg(static_cast<const __half*>(bias) + col));
+  return __ldg(static_cast<const float*>(bias) + col);
+}
 
 template <int DEPTH, int ALGO, typename TP>
 __global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 3) combine_kernel(const CombineKernelParams p) {
@@ -58,6 +65,10 @@ __global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 3) combine_kernel(const 
   for (int r = 0; r < NQ; ++r) {
     const int64_t crow = sched::block_row(DEPTH, r) * p.Mb + row;
     const int64_t ccol = sched::block_col(DEPTH, r) * Nb + cv * VEC;
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[r][i] += bias_at(p.bias, p.out_dtype, ccol + i);
+    }
     const int64_t off = static_cast<int64_t>(blockIdx.y) * p.strideC + crow * p.ldc + ccol;
     if (p.out_dtype == B200S_BF16)
       store_out<__nv_bfloat16, VEC>(static_cast<__nv_bfloat16*>(p.C) + off, acc[r], p.beta != 0, p.vec_ok != 0);
@@ -80,6 +91,7 @@ int launch_one(const CombineArgs& a, cudaStream_t stream) {
   kp.strideC = a.strideC;
   kp.out_dtype = a.out_dtype;
   kp.beta = a.beta;
+  kp.bias = a.bias;
   const size_t oes = dtype_size(a.out_dtype);
   kp.vec_ok = ((reinterpret_cast<uintptr_t>(a.C) & 15u) == 0) && ((a.ldc * oes) % 16 == 0) &&
               ((a.Nb * oes) % 16 == 0) && (a.batch == 1 || (a.strideC * oes) % 16 == 0);

@@ -49,6 +49,9 @@ struct GemmArgs {
   // TMA-store epilogue: beta 0, 16-byte aligned rows). Destinations may be peer GPUs' memory.
   int n_dst = 0;
   void* const* C_list = nullptr;
+  // Optional: a row vector of N elements of out_dtype added to every row of the product before the
+  // result is rounded (the bias of a Linear layer).
+  const void* bias = nullptr;
   // Optional: an NVLS multicast address of C(0,0) that maps to every GPU's copy. C (or C_list[0])
   // is then this GPU's own copy, written by TMA, and every tile is also stored once to mc_dst.
   void* mc_dst = nullptr;
@@ -110,6 +113,7 @@ struct CombineArgs {
   int64_t Mb, Nb, ldc;
   int64_t batch, strideC;
   int algo, depth, prod_dtype, out_dtype, beta;
+  const void* bias = nullptr;  // optional: N = 2^depth * Nb elements of out_dtype, added to every row before the rounding
 };
 int launch_combine(const CombineArgs& a, cudaStream_t stream);
 // The same recombination written to n_dst (<= 8) copies of C at once (a.C and a.beta are ignored).

@@ -50,6 +50,7 @@ struct GemmKernelParams {
   int32_t tma_store;          // 1: the epilogue stages tiles in shared memory and stores them with TMA
   int32_t n_dst;              // copies of C the TMA-store epilogue writes (1 unless the product is exchanged)
   uint8_t* dst[8];            // their (0,0) elements; copy 0 is stored by TMA, the others by ordinary stores
+  const void* bias;           // optional row vector (N elements of out_dtype) added before the rounding
   uint8_t* mc;                // or: one NVLS multicast address that reaches every GPU's copy (then n_dst == 2)
   int64_t ldc, strideC;
   void* C;
@@ -228,6 +229,23 @@ __device__ __forceinline__ __half cvt_out<__half>(float v) {
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+// Adds the bias entries of columns [col, col + 32) (those below N) to 32 fp32 accumulator words.
+__device__ __forceinline__ void add_bias32(uint32_t (&r)[32], const void* bias, int out_dt, int col, int N) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (col + j < N) {
+      float b;
+      if (out_dt == B200S_BF16)
+        b = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + col + j));
+      else if (out_dt == B200S_FP16)
+        b = __half2float(__ldg(static_cast<const __half*>(bias) + col + j));
+      else
+        b = __ldg(static_cast<const float*>(bias) + col + j);
+      r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+    }
+  }
+}
 
 // Writes 32 consecutive columns of one row. `ncols` (<= 32) of them are inside the matrix.
 template <typename OutT>
@@ -612,6 +630,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
           ptx::tmem_ld_wait();
+          if (p.bias != nullptr) add_bias32(r, p.bias, out_dt, col0 + c * 32, p.N);
           if (out_dt == B200S_BF16) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
@@ -647,6 +666,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint32_t h[32];
           ptx::tmem_ld_32x32(taddr + gc, h);
           ptx::tmem_ld_wait();
+          if (p.bias != nullptr) add_bias32(h, p.bias, out_dt, col0 + gc, p.N);
           stage_and_store(h, gc);
         }
       } else {
@@ -659,6 +679,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           ptx::tmem_ld_wait();
           const int col = col0 + c * 32;
           const int ncols = min(32, p.N - col);
+          if (p.bias != nullptr) add_bias32(r, p.bias, out_dt, col, p.N);
           if (row < p.M && ncols > 0) {
             if (out_dt == B200S_BF16)
               store_row32(reinterpret_cast<__nv_bfloat16*>(crow) + col, r, ncols, vec_ok, p.beta != 0);
@@ -901,6 +922,7 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   }
 
   GemmKernelParams& kp = out->kp;
+  kp.bias = g.bias;
   kp.tma_store = tma_store ? 1 : 0;
   kp.n_dst = kp.mc ? 2 : n_dst;
   kp.M = static_cast<int32_t>(g.M);

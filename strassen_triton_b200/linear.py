@@ -57,11 +57,13 @@ class LinearStrassen(nn.Linear):
                 depth -= 1
             if depth == 0:
                 algo = "dense"
-        out = ops.matmul_autograd(x, w.t(), algo, depth)  # weight.T stays a view (model/layers.py:252)
-        out = out.view(*batch_dims, self.out_features)
+        # weight.T stays a view (model/layers.py:252); the bias rides in the product's epilogue
+        # instead of a separate pass over the output (model/layers.py:271-272)
         if self.bias is not None:
-            out = out + self.bias.to(out.dtype)
-        return out
+            out = ops.linear_autograd(x, w.t(), self.bias, algo, depth)
+        else:
+            out = ops.matmul_autograd(x, w.t(), algo, depth)
+        return out.view(*batch_dims, self.out_features)
 
 
 def replace_linear_with_strassen(module: nn.Module, min_size: int = 128, depth: int = 1):

@@ -123,9 +123,15 @@ def resolve(p: "_lib.Problem"):
 
 def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto", depth=-1, beta=0,
                prod_dtype=None, precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0,
-               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """C = A @ B (beta=0) or C += A @ B (beta=1) on the current CUDA stream. Returns C."""
+               workspace: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ B (beta=0) or C += A @ B (beta=1) on the current CUDA stream, plus ``bias`` (N elements
+    of C's dtype, added to every row before the rounding) when given. Returns C."""
     _require_cuda(A, B, C)
+    if bias is not None:
+        _require_cuda(bias)
+        if bias.dim() != 1 or bias.shape[0] != B.shape[-1] or A.dim() != 2:
+            raise ValueError("bias must hold one element per column of a 2-D product")
+        bias = bias.to(C.dtype).contiguous()
     lib = _lib.load()
     p, A2, B2 = make_problem(A, B, C, algo, depth, beta, prod_dtype, precision, tile_variant, pipeline, b_blocks_ready,
                              fuse)
@@ -137,8 +143,12 @@ def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto"
                 workspace = torch.empty(need, dtype=torch.uint8, device=C.device)
             ws_ptr = workspace.data_ptr()
         stream = torch.cuda.current_stream(C.device).cuda_stream
-        rc = lib.b200s_matmul(ctypes.byref(p), A2.data_ptr(), B2.data_ptr(), C.data_ptr(), ws_ptr,
-                              need if need else 0, stream)
+        if bias is None:
+            rc = lib.b200s_matmul(ctypes.byref(p), A2.data_ptr(), B2.data_ptr(), C.data_ptr(), ws_ptr,
+                                  need if need else 0, stream)
+        else:
+            rc = lib.b200s_matmul_bias(ctypes.byref(p), A2.data_ptr(), B2.data_ptr(), bias.data_ptr(), C.data_ptr(),
+                                       ws_ptr, need if need else 0, stream)
         _lib.check(rc)
         if workspace is not None:
             workspace.record_stream(torch.cuda.current_stream(C.device))
@@ -146,14 +156,15 @@ def matmul_out(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *, algo="auto"
 
 
 def matmul(A: torch.Tensor, B: torch.Tensor, *, algo="auto", depth=-1, out_dtype=None, prod_dtype=None,
-           precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0, workspace=None) -> torch.Tensor:
-    """A @ B as a new tensor of ``out_dtype`` (default: the operand dtype)."""
+           precision=None, tile_variant=0, pipeline=0, b_blocks_ready=False, fuse=0, workspace=None,
+           bias=None) -> torch.Tensor:
+    """A @ B (+ bias) as a new tensor of ``out_dtype`` (default: the operand dtype)."""
     _require_cuda(A, B)
     shape = (A.shape[-2], B.shape[-1]) if A.dim() == 2 else (A.shape[0], A.shape[-2], B.shape[-1])
     C = torch.empty(shape, dtype=out_dtype or A.dtype, device=A.device)
     return matmul_out(A, B, C, algo=algo, depth=depth, beta=0, prod_dtype=prod_dtype, precision=precision,
                       tile_variant=tile_variant, pipeline=pipeline, b_blocks_ready=b_blocks_ready, fuse=fuse,
-                      workspace=workspace)
+                      workspace=workspace, bias=bias)
 
 
 def device_status(device=None):
@@ -188,31 +199,96 @@ def stage_timing(max_calls: int = 256):
         out["calls"] = calls.value
 
 
-class _MatmulFn(torch.autograd.Function):
-    """Y = X @ W with dX = dY @ W^T and dW = X^T @ dY through the same entry point. The
-    reference has no custom Function: autograd differentiates its slice/add/mm graph
+# ---- the differentiable product as a torch.library custom op ------------------------------------
+# The reference wraps its layers and whole models in torch.compile (main_profiling.py:130-144,
+# modded_nanogpt/data_dist_train_gpt2.py:721); its own matmuls are plain torch ops that dynamo traces
+# through. A ctypes call cannot be traced, so the product is registered as an opaque operator with a
+# shape-only (fake) implementation and an autograd formula: dynamo and AOT autograd then carry it
+# through a compiled graph without a graph break, forward and backward.
+_DT_NAME = {None: "", torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}
+_NAME_DT = {v: k for k, v in _DT_NAME.items()}
+
+
+@torch.library.custom_op("b200s::matmul", mutates_args=())
+def _matmul_op(X: torch.Tensor, W: torch.Tensor, algo: str, depth: int, prod_dtype: str) -> torch.Tensor:
+    return matmul(X, W, algo=algo, depth=depth, prod_dtype=_NAME_DT[prod_dtype])
+
+
+@_matmul_op.register_fake
+def _(X, W, algo, depth, prod_dtype):
+    shape = (X.shape[-2], W.shape[-1]) if X.dim() == 2 else (X.shape[0], X.shape[-2], W.shape[-1])
+    return X.new_empty(shape)
+
+
+def _matmul_setup(ctx, inputs, output):
+    X, W, algo, depth, prod_dtype = inputs
+    ctx.save_for_backward(X, W)
+    ctx.cfg = (algo, depth, prod_dtype)
+
+
+def _matmul_backward(ctx, dY):
+    """dX = dY @ W^T and dW = X^T @ dY through the same operator, with transposed views (no copies).
+    The reference has no custom backward: autograd differentiates its slice/add/mm graph
     (fixed_strassen_fp32_agg.py:13-125), which computes these same two products."""
+    X, W = ctx.saved_tensors
+    algo, depth, prod_dtype = ctx.cfg
+    dX = dW = None
+    if dY.dtype != X.dtype:
+        dY = dY.to(X.dtype)
+    if ctx.needs_input_grad[0]:
+        dX = _matmul_op(dY, W.transpose(-1, -2), algo, depth, prod_dtype)
+    if ctx.needs_input_grad[1]:
+        dW = _matmul_op(X.transpose(-1, -2), dY, algo, depth, prod_dtype)
+    return dX, dW, None, None, None
 
-    @staticmethod
-    def forward(ctx, X, W, algo, depth, prod_dtype):
-        ctx.save_for_backward(X, W)
-        ctx.cfg = (algo, depth, prod_dtype)
-        return matmul(X, W, algo=algo, depth=depth, prod_dtype=prod_dtype)
 
-    @staticmethod
-    def backward(ctx, dY):
-        X, W = ctx.saved_tensors
-        algo, depth, prod_dtype = ctx.cfg
-        dX = dW = None
-        if dY.dtype != X.dtype:
-            dY = dY.to(X.dtype)
-        if ctx.needs_input_grad[0]:
-            dX = matmul(dY, W.transpose(-1, -2), algo=algo, depth=depth, prod_dtype=prod_dtype)
-        if ctx.needs_input_grad[1]:
-            dW = matmul(X.transpose(-1, -2), dY, algo=algo, depth=depth, prod_dtype=prod_dtype)
-        return dX, dW, None, None, None
+_matmul_op.register_autograd(_matmul_backward, setup_context=_matmul_setup)
+
+
+@torch.library.custom_op("b200s::linear", mutates_args=())
+def _linear_op(X: torch.Tensor, W: torch.Tensor, bias: torch.Tensor, algo: str, depth: int) -> torch.Tensor:
+    """X @ W + bias with the bias added in the product's epilogue (X 2-D, W given as weight.T)."""
+    if depth > 2:      # the recursion above two levels has no epilogue of its own to carry the bias
+        return matmul(X, W, algo=algo, depth=depth) + bias.to(X.dtype)
+    return matmul(X, W, algo=algo, depth=depth, bias=bias)
+
+
+@_linear_op.register_fake
+def _(X, W, bias, algo, depth):
+    return X.new_empty((X.shape[0], W.shape[1]))
+
+
+def _linear_setup(ctx, inputs, output):
+    X, W, bias, algo, depth = inputs
+    ctx.save_for_backward(X, W)
+    ctx.cfg = (algo, depth, bias.dtype)
+
+
+def _linear_backward(ctx, dY):
+    X, W = ctx.saved_tensors
+    algo, depth, bias_dtype = ctx.cfg
+    dX = dW = db = None
+    if ctx.needs_input_grad[2]:
+        db = dY.sum(0).to(bias_dtype)
+    if dY.dtype != X.dtype:
+        dY = dY.to(X.dtype)
+    if ctx.needs_input_grad[0]:
+        dX = _matmul_op(dY, W.transpose(-1, -2), algo, depth, "")
+    if ctx.needs_input_grad[1]:
+        dW = _matmul_op(X.transpose(-1, -2), dY, algo, depth, "")
+    return dX, dW, db, None, None
+
+
+_linear_op.register_autograd(_linear_backward, setup_context=_linear_setup)
+
+
+def linear_autograd(X, W, bias, algo="auto", depth=-1):
+    """Differentiable X @ W + bias (X 2-D, W = weight.T as a view), the bias fused into the epilogue."""
+    _require_cuda(X, W, bias)
+    return _linear_op(X, W, bias, algo, int(depth))
 
 
 def matmul_autograd(X, W, algo="auto", depth=-1, prod_dtype=None):
-    """Differentiable X @ W (2-D operands)."""
-    return _MatmulFn.apply(X, W, algo, depth, prod_dtype)
+    """Differentiable X @ W (2-D or batched 3-D operands); traceable by torch.compile."""
+    _require_cuda(X, W)
+    return _matmul_op(X, W, algo, int(depth), _DT_NAME[prod_dtype])

@@ -178,6 +178,12 @@ class PeerShardedMatmul:
         self.exchange = exchange
         self.rows = M // self.world
         self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        if algo == "auto" and self.world >= 4:
+            # The tuner table is measured on one GPU, where a Strassen block is a few per cent ahead of
+            # a dense one at these shapes; sharded, its exchange (the recombination kernel's stores)
+            # runs after the products while a dense block's exchange runs under them. Measured at
+            # 32768^3: 8 ranks 7.4 ms dense against 9.7 ms two-level; 2 ranks 27.0 against 25.1.
+            algo, depth = "dense", 0
         # what the library would run for one panel (its tuner table, or the caller's choice) decides
         # how many panels fit: fewer when the rows of a panel do not split as the depth needs
         while True:

@@ -20,30 +20,40 @@ _ALGO_NAME = {_lib.ALGO_DENSE: "dense", _lib.ALGO_CLASSIC: "classic", _lib.ALGO_
 _DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float32: _lib.FP32}
 
 
-def _time(fn, reps: int) -> float:
-    """Milliseconds per call over `reps` back-to-back calls (CUDA events around the whole run), best
-    of three such runs after warm-up: the regime of a training loop or of bench.py, where host-side
-    launch work is hidden behind the previous call."""
+def _time(fn, seconds: float) -> float:
+    """Milliseconds per call in the sustained regime: back-to-back calls for `seconds`, mean over the
+    second half of the run. A B200 runs a dense product against its power limit, and the first few
+    tens of milliseconds after an idle gap are faster than anything a training loop or a serving
+    process will see; a table measured there would pick schedules that lose under load."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
-    best = float("inf")
-    for _ in range(3):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
+    events = [torch.cuda.Event(enable_timing=True)]
+    events[0].record()
+    import time
+
+    t0 = time.time()
+    while True:
+        for _ in range(5):
             fn()
-        e1.record()
-        torch.cuda.synchronize()
-        best = min(best, e0.elapsed_time(e1) / reps)
-    return best
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        events.append(e)
+        if len(events) > 3:
+            events[-3].synchronize()
+        if time.time() - t0 >= seconds:
+            break
+    torch.cuda.synchronize()
+    per = [events[i].elapsed_time(events[i + 1]) / 5 for i in range(len(events) - 1)]
+    tail = per[len(per) // 2:]
+    return sum(tail) / len(tail)
 
 
 _SCHEDULES = {2: "separate", 3: "fused"}      # b200s_problem.fuse values the sweep tries
 
 
-def sweep(shapes: Iterable[Tuple[int, int, int]], dtype=torch.bfloat16, reps: int = 5, algos=("classic", "winograd"),
-          verbose: bool = True):
+def sweep(shapes: Iterable[Tuple[int, int, int]], dtype=torch.bfloat16, seconds: float = 0.6,
+          algos=("classic", "winograd"), verbose: bool = True):
     """Measure every candidate for each (M, N, K) and record the fastest. Candidates: the dense
     product, and each Strassen algorithm at depth 1 and 2 under both schedules (separate passes, and
     the fused kernel with the last quadrant recombined after it). Returns the rows."""
@@ -62,7 +72,7 @@ def sweep(shapes: Iterable[Tuple[int, int, int]], dtype=torch.bfloat16, reps: in
             p, _, _ = ops.make_problem(A, B, C, algo, d, fuse=fuse, pipeline=2 if fuse == 2 else 0)
             ws = torch.empty(max(ops.workspace_bytes(p), 1), dtype=torch.uint8, device="cuda")
             timings[(algo, d, fuse)] = _time(lambda: ops.matmul_out(A, B, C, algo=algo, depth=d, fuse=fuse,
-                                                                    pipeline=2 if fuse == 2 else 0, workspace=ws), reps)
+                                                                    pipeline=2 if fuse == 2 else 0, workspace=ws), seconds)
         (algo, d, fuse), ms = min(timings.items(), key=lambda kv: kv[1])
         _lib.check(lib.b200s_tuner_record_schedule(M, N, K, _DT[dtype], ops._ALGO[algo], d, fuse))
         rows.append((M, N, K, algo, d, fuse, ms, timings))
@@ -95,3 +105,26 @@ def lookup(M: int, N: int, K: int, dtype=torch.bfloat16) -> Tuple[str, int]:
     a, d = ctypes.c_int32(0), ctypes.c_int32(0)
     _lib.check(_lib.load().b200s_tuner_lookup(M, N, K, _DT[dtype], ctypes.byref(a), ctypes.byref(d)))
     return _ALGO_NAME[a.value], d.value
+
+
+# Shapes of the shipped table: cubes around the crossover, the GPT-2-124M Linear shapes, and the
+# per-rank blocks of the row-sharded 32768^3 product at 8, 4, 2 and 1 ranks.
+DEFAULT_SHAPES = [(2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 768, 3072), (8192, 3072, 768),
+                  (8192, 2304, 768), (12288, 12288, 12288), (16384, 16384, 16384), (4096, 32768, 32768),
+                  (8192, 32768, 32768), (16384, 32768, 32768), (32768, 32768, 32768)]
+
+
+def main():
+    """Regenerates the shipped table on the current GPU: ``python -m strassen_triton_b200.tuner [path]``."""
+    import sys
+
+    path = sys.argv[1] if len(sys.argv) > 1 else DEFAULT_TABLE
+    _lib.check(_lib.load().b200s_tuner_clear())
+    sweep(DEFAULT_SHAPES, torch.bfloat16)
+    sweep([(4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384)], torch.float16, algos=("classic",))
+    save(path)
+    print(f"saved {path}")
+
+
+if __name__ == "__main__":
+    main()

@@ -67,7 +67,7 @@ def test_stage_timing_covers_the_call(lib, fuse):
     """The four stage durations of the measured calls add up to (almost) the duration of the calls."""
     from strassen_triton_b200 import ops
 
-    n = 2048
+    n = 8192                                            # large enough for launch gaps not to matter
     g = torch.Generator(device="cuda").manual_seed(0)
     A = (torch.rand((n, n), generator=g, device="cuda") * 2 - 1).bfloat16()
     B = (torch.rand((n, n), generator=g, device="cuda") * 2 - 1).bfloat16()
@@ -87,8 +87,12 @@ def test_stage_timing_covers_the_call(lib, fuse):
     assert stages["calls"] == 5
     parts = [stages[k] for k in ("operand_blocks_A", "operand_blocks_B", "products", "recombination")]
     assert all(x >= 0 for x in parts) and parts[2] > 0
-    assert 0.7 * total <= sum(parts) <= 1.05 * total
-    ops.matmul_out(A, B, C, algo="dense")               # a schedule that records nothing
-    with ops.stage_timing(2) as none:
+    assert 0.8 * total <= sum(parts) <= 1.05 * total
+    ops.matmul_out(A, B, C, algo="dense")
+    with ops.stage_timing(2) as dense:                  # a dense product is all "products"
         ops.matmul_out(A, B, C, algo="dense")
+    assert dense["calls"] == 1 and dense["products"] > 0
+    assert dense["operand_blocks_A"] + dense["operand_blocks_B"] + dense["recombination"] < 0.05 * dense["products"]
+    with ops.stage_timing(2) as none:                   # the multi-stream schedule records nothing
+        ops.matmul_out(A, B, C, algo="classic", depth=2, fuse=2, pipeline=1)
     assert none["calls"] == 0
