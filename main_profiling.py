@@ -3,7 +3,10 @@ main_profiling.py:94-302): ``LinearStrassen`` against ``nn.Linear`` for square l
 several depths, with the same columns - time of the standard layer, time of the Strassen layer,
 speed-up, TFLOP/s by the standard count 2*N^3, max-abs difference and allclose - measured with CUDA
 events after warm-up (the reference uses ``triton.testing.do_bench`` on ``torch.compile``d layers; no
-compiler is involved here, ``nn.Linear`` is cuBLAS and ``LinearStrassen`` is this library).
+compiler is involved here, ``nn.Linear`` is cuBLAS and ``LinearStrassen`` is this library). A third
+timing column shows how the reference itself computes the layer on this GPU: the torch-level Strassen
+recursion (slices, elementwise sums in fp32, ``torch.mm`` sub-products) of
+fixed_strassen_fp32_agg.py:13-125, restated below as the baseline ``torch_strassen``.
 
     python main_profiling.py [--sizes 4096 8192 16384] [--depths 1 2] [--dtype bf16] [--reps 20]
 """
@@ -34,6 +37,28 @@ def bench_ms(fn, warmup, reps):
     return times[0], sum(times) / len(times)
 
 
+def torch_strassen(A, B, depth, dtype):
+    """Baseline only: Strassen as the reference runs it, with torch ops (eight quadrant views widened to
+    fp32, ten sums rounded to `dtype`, seven torch.mm, eight fp32 sums, two concatenations per level)."""
+    n = A.shape[0]
+    if depth == 0 or n <= 16:
+        return torch.mm(A.to(dtype), B.to(dtype))
+    m = n // 2
+    a11, a12, a21, a22 = (A[:m, :m].float(), A[:m, m:].float(), A[m:, :m].float(), A[m:, m:].float())
+    b11, b12, b21, b22 = (B[:m, :m].float(), B[:m, m:].float(), B[m:, :m].float(), B[m:, m:].float())
+    mul = lambda x, y: torch_strassen(x.to(dtype), y.to(dtype), depth - 1, dtype).float()  # noqa: E731
+    m1 = mul(a11 + a22, b11 + b22)
+    m2 = mul(a21 + a22, b11)
+    m3 = mul(a11, b12 - b22)
+    m4 = mul(a22, b21 - b11)
+    m5 = mul(a11 + a12, b22)
+    m6 = mul(a21 - a11, b11 + b12)
+    m7 = mul(a12 - a22, b21 + b22)
+    top = torch.cat((m1 + m4 - m5 + m7, m3 + m5), dim=1)
+    bottom = torch.cat((m2 + m4, m1 - m2 + m3 + m6), dim=1)
+    return torch.cat((top, bottom), dim=0).to(dtype)
+
+
 def benchmark_linear_layers(N, depth, dtype, reps):
     """One row of the table: a D x D input through nn.Linear(D, D) and LinearStrassen(D, D, depth)."""
     std = nn.Linear(N, N, bias=False, device="cuda", dtype=dtype)
@@ -46,24 +71,28 @@ def benchmark_linear_layers(N, depth, dtype, reps):
         close = torch.allclose(y_std.float(), y_str.float(), rtol=5e-2, atol=5e-2 * y_std.float().abs().max().item())
         std_min, std_mean = bench_ms(lambda: std(x), 5, reps)
         str_min, str_mean = bench_ms(lambda: strassen(x), 5, reps)
+        wt = std.weight.t()
+        ref_min, ref_mean = bench_ms(lambda: torch_strassen(x, wt, depth, dtype), 2, max(3, reps // 4))
     flops = 2.0 * N ** 3
-    return {"N": N, "depth": depth, "std_ms": std_mean, "strassen_ms": str_mean, "speedup": std_mean / str_mean,
-            "std_tflops": flops / std_min / 1e9, "strassen_tflops": flops / str_min / 1e9, "max_abs_diff": max_diff,
-            "allclose": close}
+    return {"N": N, "depth": depth, "std_ms": std_mean, "strassen_ms": str_mean, "torch_strassen_ms": ref_mean,
+            "speedup": std_mean / str_mean, "speedup_vs_torch_strassen": ref_mean / str_mean,
+            "std_tflops": flops / std_min / 1e9, "strassen_tflops": flops / str_min / 1e9,
+            "torch_strassen_tflops": flops / ref_min / 1e9, "max_abs_diff": max_diff, "allclose": close}
 
 
 def profile_linear_layers(sizes, depths, dtype, reps):
     rows = []
-    print(f"{'N':>6} {'depth':>5} {'std ms':>9} {'strassen ms':>12} {'speedup':>8} {'std TF/s':>9} {'str TF/s':>9} "
-          f"{'max|diff|':>10} allclose")
+    print(f"{'N':>6} {'depth':>5} {'std ms':>9} {'strassen ms':>12} {'torch-str ms':>13} {'speedup':>8} {'std TF/s':>9} "
+          f"{'str TF/s':>9} {'t-str TF/s':>10} {'max|diff|':>10} allclose")
     for N in sizes:
         for depth in depths:
             if N % (8 << depth):
                 continue
             r = benchmark_linear_layers(N, depth, dtype, reps)
             rows.append(r)
-            print(f"{r['N']:6d} {r['depth']:5d} {r['std_ms']:9.3f} {r['strassen_ms']:12.3f} {r['speedup']:8.3f} "
-                  f"{r['std_tflops']:9.1f} {r['strassen_tflops']:9.1f} {r['max_abs_diff']:10.3e} {r['allclose']}")
+            print(f"{r['N']:6d} {r['depth']:5d} {r['std_ms']:9.3f} {r['strassen_ms']:12.3f} {r['torch_strassen_ms']:13.3f} "
+                  f"{r['speedup']:8.3f} {r['std_tflops']:9.1f} {r['strassen_tflops']:9.1f} {r['torch_strassen_tflops']:10.1f} "
+                  f"{r['max_abs_diff']:10.3e} {r['allclose']}")
     return rows
 
 

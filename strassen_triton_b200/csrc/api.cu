@@ -7,7 +7,6 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -398,16 +397,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
   const int prof = prof_new_call();
   prof_mark(prof, 0, stream);
 
-#ifdef B200S_FUSED_TRACE
-  // development build: the kernel leaves timestamps of CTA 0 behind the counters (the scratch is
-  // then over-allocated by the caller); environment switches take work out of the kernel
   B200S_CUDA_OK(cudaMemsetAsync(flags, 0, 64, stream));
-  const char* dbg_env = std::getenv("B200S_FUSED_DEBUG");
-  const int dbg = dbg_env ? std::atoi(dbg_env) : 0;
-#else
-  B200S_CUDA_OK(cudaMemsetAsync(flags, 0, 64, stream));
-  const int dbg = 0;
-#endif
 
   PreaddOuterArgs pa;
   pa.batch = 1, pa.strideX = 0;
@@ -430,26 +420,12 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
     if (rc) return rc;
   }
   prof_mark(prof, 2, stream);
-  int formed = 1;
-  if (dbg & 1) {
-    // every group formed before the kernel
-    for (int i = 1; i < 7; ++i) {
-      pa.groups[0] = order[i], pa.out_block0[0] = i * np2;
-      pb.groups[0] = order[i], pb.out_block0[0] = i * np2;
-      rc = launch_preadd_outer(pa, stream);
-      if (rc) return rc;
-      if (!p->b_blocks_ready) rc = launch_preadd_outer(pb, stream);
-      if (rc) return rc;
-    }
-    formed = 7;
-  }
-
   int last_pos[4], tail_mask = 0;
   for (int r = 0; r < 4; ++r) {
     last_pos[r] = 0;
     for (int p1 = 0; p1 < 7; ++p1)
       if (sched::w1(sa, r, p1) != 0 && pos[p1] > last_pos[r]) last_pos[r] = pos[p1];
-    if ((tail_outside && last_pos[r] == 6) || (dbg & 2)) tail_mask |= 1 << r;
+    if (tail_outside && last_pos[r] == 6) tail_mask |= 1 << r;
   }
 
   FusedArgs f;
@@ -467,7 +443,7 @@ int run_fused(const b200s_problem* p, const Plan& plan, const void* A, const voi
   f.b_rows_blk = pb.rows_blk, f.b_cols_blk = pb.cols_blk, f.b_transposed = pb.transposed;
   f.C = C, f.Mb = plan.Mb, f.Nb = plan.Nb, f.ldc = p->ldc, f.out_dtype = p->out_dtype, f.beta = p->beta;
   for (int i = 0; i < 7; ++i) f.order[i] = order[i];
-  f.groups_formed = formed;
+  f.groups_formed = 1;
   f.b_formed = p->b_blocks_ready ? 1 : 0;
   f.quads_inside = 0xf & ~tail_mask;
   f.flags = flags;

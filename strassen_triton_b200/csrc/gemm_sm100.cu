@@ -144,10 +144,6 @@ template <class F>
 __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile uint32_t* abort_word, int tid) {
   constexpr int INNER = F::kInner, ALGO = F::kAlgo;
   using T = typename F::Elem;
-#ifdef B200S_FUSED_TRACE
-  const uint64_t trace_t0 = ptx::global_timer_ns();
-  const bool tracer = blockIdx.x == 0 && (tid & 63) == 0;
-#endif
   // ---- phase 1: operand blocks
   if (fz.b_formed || tid < 64) {
     const int team = fz.b_formed ? kAdderThreads : 64;
@@ -157,9 +153,6 @@ __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile
     for (int i = fz.groups_formed; i < 7; ++i) {
       adder_preadd<INNER, ALGO, sched::kSideA, T>(fz.pre[0], i, first, stride);
       adder_signal(fz.flags + i, 2, team, tid == 0);
-#ifdef B200S_FUSED_TRACE
-      if (tracer) fz.flags[64 + i] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
-#endif
     }
   } else {
     const int64_t first = static_cast<int64_t>(blockIdx.x) * 64 + (tid - 64);
@@ -168,9 +161,6 @@ __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile
     for (int i = fz.groups_formed; i < 7; ++i) {
       adder_preadd<INNER, ALGO, sched::kSideB, T>(fz.pre[1], i, first, stride);
       adder_signal(fz.flags + i, 3, 64, tid == 64);
-#ifdef B200S_FUSED_TRACE
-      if (tracer) fz.flags[72 + i] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
-#endif
     }
   }
   // ---- phase 2: quadrants of C
@@ -187,13 +177,7 @@ __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile
     }
     ptx::named_bar_sync(1, kAdderThreads);
     if (*abort_word != 0) break;
-#ifdef B200S_FUSED_TRACE
-    if (tracer && tid == 0) fz.flags[80 + t] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
-#endif
     adder_combine<INNER, ALGO, T>(fz.comb, fz.comb_quad[t], first, stride);
-#ifdef B200S_FUSED_TRACE
-    if (tracer && tid == 0) fz.flags[88 + t] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_t0) / 1000);
-#endif
   }
 }
 
@@ -390,9 +374,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool alive = true;
       [[maybe_unused]] int group_ready = 0;
       if constexpr (F::kOn) group_ready = fz.groups_formed;
-#ifdef B200S_FUSED_TRACE
-      const uint64_t trace_p0 = ptx::global_timer_ns();
-#endif
       int it = 0;
       for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters, ++it) {
         int b, mt, nt;
@@ -405,19 +386,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           // first tile of a new outer group: every CTA's adders must have stored its operand blocks
           const int g = b / fz.np2;
           if (g >= group_ready) {
-#ifdef B200S_FUSED_TRACE
-            const uint64_t w0 = ptx::global_timer_ns();
-#endif
             if (!ptx::wait_counter(fz.flags + g, fz.ready_target * gridDim.x, abort_word, kWhoProducerGroup)) {
               alive = false;
               break;
             }
-#ifdef B200S_FUSED_TRACE
-            if (blockIdx.x == 0) {
-              fz.flags[32 + g] = static_cast<uint32_t>((ptx::global_timer_ns() - w0) / 1000);       // stall, us
-              fz.flags[40 + g] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_p0) / 1000); // group start, us
-            }
-#endif
             ptx::fence_proxy_async_all();
             group_ready = g + 1;
           }
@@ -465,10 +437,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
-#ifdef B200S_FUSED_TRACE
-      if constexpr (F::kOn)
-        if (blockIdx.x == 0) fz.flags[48] = static_cast<uint32_t>((ptx::global_timer_ns() - trace_p0) / 1000);
-#endif
     }
     __syncwarp();
   } else if (warp == 1) {

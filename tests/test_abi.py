@@ -161,3 +161,54 @@ def test_corrupt_or_missing_table_leaves_state_untouched(lib, tmp_path):
 
 def test_launch_count_starts_at_zero_without_a_gpu(lib):
     assert lib.b200s_launch_count() >= 0
+
+
+def test_tuner_table_carries_the_schedule(lib, tmp_path):
+    lib.b200s_tuner_clear()
+    a, d, f = ctypes.c_int32(0), ctypes.c_int32(0), ctypes.c_int32(9)
+    assert lib.b200s_tuner_lookup_schedule(16384, 16384, 16384, _lib.BF16, ctypes.byref(a), ctypes.byref(d),
+                                           ctypes.byref(f)) == 0
+    assert f.value == 0                                           # nothing recorded: the built-in rule applies
+    assert lib.b200s_tuner_record_schedule(16384, 16384, 16384, _lib.BF16, _lib.ALGO_CLASSIC, 2, 3) == 0
+    assert lib.b200s_tuner_record_schedule(4096, 4096, 4096, _lib.BF16, _lib.ALGO_DENSE, 0, 3) == 0
+    assert lib.b200s_tuner_record_schedule(8192, 8192, 8192, _lib.BF16, _lib.ALGO_CLASSIC, 1, 7) == _lib.ERR_BAD_SHAPE
+    old = tmp_path / "six_columns.txt"
+    old.write_text("# M N K in_dtype algo depth\n8192 8192 8192 0 3 1\n")
+    new = str(tmp_path / "seven.txt").encode()
+    assert lib.b200s_tuner_save(new) == 0
+    lib.b200s_tuner_clear()
+    assert lib.b200s_tuner_load(new) == 0
+    for shape, want in (((16384, 16384, 16384), (_lib.ALGO_CLASSIC, 2, 3)), ((4096, 4096, 4096), (_lib.ALGO_DENSE, 0, 0))):
+        assert lib.b200s_tuner_lookup_schedule(*shape, _lib.BF16, ctypes.byref(a), ctypes.byref(d), ctypes.byref(f)) == 0
+        assert (a.value, d.value, f.value) == want                # a dense entry has no schedule
+    assert lib.b200s_tuner_load(str(old).encode()) == 0           # tables without the column still load
+    assert lib.b200s_tuner_lookup_schedule(8192, 8192, 8192, _lib.BF16, ctypes.byref(a), ctypes.byref(d),
+                                           ctypes.byref(f)) == 0
+    assert (a.value, d.value, f.value) == (_lib.ALGO_WINOGRAD, 1, 0)
+    lib.b200s_tuner_clear()
+
+
+def test_new_entry_points_validate_before_touching_a_device(lib):
+    p = problem()
+    assert lib.b200s_matmul_bias(ctypes.byref(p), 16, 16, None, 16, 256, 1 << 30, None) == _lib.ERR_NULL_POINTER
+    assert lib.b200s_matmul_peers(ctypes.byref(p), 16, 16, None, 2, 256, 1 << 30, None) == _lib.ERR_NULL_POINTER
+    dst = (ctypes.c_void_p * 2)(16, 32)
+    assert lib.b200s_matmul_peers(ctypes.byref(p), 16, 16, dst, 9, 256, 1 << 30, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_matmul_peers(ctypes.byref(problem(beta=1)), 16, 16, dst, 2, 256, 1 << 30, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_matmul_multicast(ctypes.byref(p), 16, 16, 16, None, 256, 1 << 30, None) == _lib.ERR_NULL_POINTER
+    # the multicast store lives in the dense epilogue: a Strassen problem is refused
+    assert lib.b200s_matmul_multicast(ctypes.byref(p), 16, 16, 16, 32, 256, 1 << 30, None) == _lib.ERR_BAD_ALGO
+    assert lib.b200s_peer_barrier(None, 0, 2, 1, 1000, None) == _lib.ERR_NULL_POINTER
+    assert lib.b200s_peer_barrier(dst, 2, 2, 1, 1000, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_peer_barrier(dst, 0, 2, 1, 0, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_wait_probe(0, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_profile_begin(0) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_profile_end(None, None) == _lib.ERR_NULL_POINTER
+    assert lib.b200s_workspace_bytes(ctypes.byref(problem(fuse=4)), ctypes.byref(ctypes.c_size_t(0))) == _lib.ERR_BAD_SHAPE
+
+
+def test_fused_schedule_keeps_its_counters_at_the_end_of_the_scratch(lib):
+    """Every one- or two-level scratch ends with the 256 bytes of counters the fused kernel's CTAs
+    share, whatever schedule a call ends up using; the schedule itself does not change the size."""
+    sizes = {ws_bytes(lib, problem(fuse=f))[1] for f in (0, 1, 2, 3)}
+    assert len(sizes) == 1 and sizes.pop() == 3 * 49 * 256 * 256 * 2 + FLAGS

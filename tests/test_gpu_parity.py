@@ -403,3 +403,19 @@ def test_workspace_too_small_raises(ops):
         ops.matmul(torch.zeros(500, 500, device="cuda", dtype=torch.bfloat16),
                    torch.zeros(500, 500, device="cuda", dtype=torch.bfloat16), algo="classic", depth=2)
     assert _lib.load().b200s_launch_count() > 0
+
+
+def test_readme_benchmark_row(ops):
+    """One row of the README benchmark table (main_profiling.py): the three timed columns are filled,
+    the two Strassen columns agree with the standard layer, and the torch-level Strassen baseline
+    computes the same product as the library's."""
+    import main_profiling
+
+    row = main_profiling.benchmark_linear_layers(1024, 2, torch.bfloat16, reps=4)
+    assert row["allclose"] and row["max_abs_diff"] < 0.25
+    assert all(row[k] > 0 for k in ("std_ms", "strassen_ms", "torch_strassen_ms", "std_tflops", "strassen_tflops"))
+    A, B = seeded_pair(3, (512, 512), (512, 512), dist="uniform")
+    A, B = A.bfloat16().cuda(), B.bfloat16().cuda()
+    base = main_profiling.torch_strassen(A, B, 2, torch.bfloat16)
+    ref = A.double() @ B.double()
+    assert rel(base, ref) < 2e-2 and rel(ops.matmul(A, B, algo="classic", depth=2), ref) < 2e-2

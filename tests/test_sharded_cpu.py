@@ -1,5 +1,5 @@
 """The row-sharded product's orchestration on CPU ranks (gloo, world size 2), with the CPU
-oracle standing in for the per-rank CUDA product."""
+torch.mm standing in for the per-rank CUDA product."""
 import os
 import socket
 
@@ -40,7 +40,6 @@ def _worker(rank, world, port, M, panels, fail_rank, q):
 
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
     try:
-        from oracle import strassen_oracle as so
         from strassen_triton_b200.sharded import sharded_matmul
 
         g = torch.Generator().manual_seed(0)
