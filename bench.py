@@ -28,7 +28,8 @@ table picks them, bf16 operands, fp32 accumulation and aggregation, bf16 result)
 * ``--impl reference``: the reference's own recursion restated for the CPU (``oracle/``) on the host
   cores; ``config`` states the product it really multiplies and ``stands_for`` the workload it samples.
 * ``--only CASE``: runs one kernel of the pipeline a few times on synthetic data and exits (for
-  profiling one kernel under ncu): gemm_grouped, dense, preadd, combine, fused.
+  profiling one kernel under ncu): gemm_grouped, cublas_grouped, dense, preadd, combine, fused. ``--quick`` keeps only
+  the timed steps and the end-to-end leg of the N = 1 run (for a launch list under ncu).
 
 Prints one JSON line (rank 0).
 """
@@ -55,8 +56,8 @@ UNIT = "TFLOP/s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the product kernel on a
 # one-kernel ncu capture of 14 products of 4096^3; a full launch of the N = 1 workload runs 49 such
 # products and its traffic grows in proportion.
-GEMM_DRAM_BYTES_14_PRODUCTS = 1.549e9 + 0.450e9
-GEMM_DRAM_SOURCE = ("ncu one-kernel capture, 14 products of 4096^3 (1.549 GB read + 0.450 GB written), "
+GEMM_DRAM_BYTES_14_PRODUCTS = 1.334e9 + 0.447e9
+GEMM_DRAM_SOURCE = ("ncu one-kernel capture, 14 products of 4096^3 (1.334 GB read + 0.447 GB written), "
                     "scaled by 49/14 to the 49 products of a launch")
 
 
@@ -323,6 +324,12 @@ def run_only(args):
         C = torch.empty_like(A)
         for _ in range(args.steps):
             ops.matmul_out(A, B, C, algo="dense")
+    elif what == "cublas_grouped":     # the same batch through cuBLAS (torch.bmm), for a side-by-side capture
+        A = torch.randn(nb, n, n, device="cuda").bfloat16()
+        B = torch.randn(nb, n, n, device="cuda").bfloat16()
+        C = torch.empty_like(A)
+        for _ in range(args.steps):
+            torch.bmm(A, B, out=C)
     elif what == "dense":
         A = torch.randn(n, n, device="cuda").bfloat16()
         B = torch.randn(n, n, device="cuda").bfloat16()
@@ -591,6 +598,9 @@ def run_gpu_arm(args):
             if rank == 0:
                 line["fsdp_step"] = fs
                 line["fsdp_twin_ok"] = twin_ok
+    elif args.quick:
+        line["stages_ms"] = {k: round(stages[k], 4) for k in stage_names}
+        line["note"] = "--quick: timed steps and end-to-end only (the short run behind the ncu launch list)"
     else:
         # ---- comparison with cuBLAS dense on the same GPU, interleaved ----
         dense = lambda: torch.mm(A, B, out=C)  # noqa: E731
@@ -718,8 +728,9 @@ def main():
                          "stores for dense blocks where available, plain peer stores otherwise); 'nccl' = all-gather of "
                          "the row blocks")
     ap.add_argument("--fsdp", type=int, default=1, help="N > 1: also time the FSDP GPT-2 step (0 = skip)")
-    ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, dense, preadd, "
-                                                 "combine, fused")
+    ap.add_argument("--quick", action="store_true", help="N = 1: skip the comparison arms (for a launch list under ncu)")
+    ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, cublas_grouped, "
+                                                 "dense, preadd, combine, fused")
     ap.add_argument("--n", type=int, default=4096, help="--only: matrix extent")
     ap.add_argument("--products", type=int, default=14, help="--only gemm_grouped: products in the batch")
     args = ap.parse_args()

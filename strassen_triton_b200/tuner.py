@@ -50,6 +50,18 @@ def _time(fn, seconds: float) -> float:
 
 
 _SCHEDULES = {2: "separate", 3: "fused"}      # b200s_problem.fuse values the sweep tries
+TIE = 1.01                                    # candidates within 1 % of the fastest count as tied
+
+
+def _pick(timings):
+    """The fastest candidate, except that among candidates within TIE of it the plainer one wins:
+    dense before Strassen (better accuracy), classic before Winograd (better accuracy), separate
+    passes before the fused kernel (one schedule fewer to reason about)."""
+    best = min(timings.values())
+    tied = [k for k, t in timings.items() if t <= TIE * best]
+    rank = lambda k: (k[0] != "dense", k[2] == 3, k[0] != "classic", k[1])  # noqa: E731
+    k = min(tied, key=rank)
+    return k, timings[k]
 
 
 def sweep(shapes: Iterable[Tuple[int, int, int]], dtype=torch.bfloat16, seconds: float = 0.6,
@@ -73,7 +85,7 @@ def sweep(shapes: Iterable[Tuple[int, int, int]], dtype=torch.bfloat16, seconds:
             ws = torch.empty(max(ops.workspace_bytes(p), 1), dtype=torch.uint8, device="cuda")
             timings[(algo, d, fuse)] = _time(lambda: ops.matmul_out(A, B, C, algo=algo, depth=d, fuse=fuse,
                                                                     pipeline=2 if fuse == 2 else 0, workspace=ws), seconds)
-        (algo, d, fuse), ms = min(timings.items(), key=lambda kv: kv[1])
+        (algo, d, fuse), ms = _pick(timings)
         _lib.check(lib.b200s_tuner_record_schedule(M, N, K, _DT[dtype], ops._ALGO[algo], d, fuse))
         rows.append((M, N, K, algo, d, fuse, ms, timings))
         if verbose:
