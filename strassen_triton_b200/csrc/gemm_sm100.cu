@@ -68,6 +68,9 @@ enum : uint32_t {
   kWhoProbe = 7           // wait_probe_kernel: the self-test of the bounded wait
 };
 
+// How long a CTA that gives up waits for its producer's outstanding TMA loads to land.
+constexpr uint64_t kDrainLimitNs = 20ull * 1000 * 1000;
+
 // ---- fused Strassen kernel: what the adder warps do ----------------------------------------------
 // Phase 1: the operand blocks of every outer group still to be formed, in processing order; warps 0-1
 // of the adder warpgroup take side A, warps 2-3 side B (all four side A when B's blocks exist already).
@@ -141,7 +144,8 @@ __device__ __forceinline__ void adder_signal(uint32_t* ready, uint32_t bar, uint
 }
 
 template <class F>
-__device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile uint32_t* abort_word, int tid) {
+__device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile uint32_t* abort_word,
+                                           volatile uint32_t* go_word, int tid) {
   constexpr int INNER = F::kInner, ALGO = F::kAlgo;
   using T = typename F::Elem;
   // ---- phase 1: operand blocks
@@ -174,9 +178,14 @@ __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile
       for (int j = 0; j < nwait; ++j)
         if (!ptx::wait_counter(fz.flags + 8 + j, fz.done_target, abort_word, kWhoAdder)) break;
       ptx::fence_proxy_async_all();  // they were written by TMA stores
+      *go_word = *abort_word == 0 ? 1u : 0u;
     }
+    // One thread decides for the team: the abort word can change at any moment (another role giving
+    // up), and threads that read it themselves could part ways and leave the rest at the barrier.
     ptx::named_bar_sync(1, kAdderThreads);
-    if (*abort_word != 0) break;
+    const bool go = *go_word != 0;
+    ptx::named_bar_sync(1, kAdderThreads);  // all have read the decision before it is written again
+    if (!go) break;
     adder_combine<INNER, ALGO, T>(fz.comb, fz.comb_quad[t], first, stride);
   }
 }
@@ -328,6 +337,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(gbase + kStages * STAGE_BYTES + STAGING_BYTES + 8 * (2 * kStages + 4));
   volatile uint32_t* abort_word = tmem_slot + 1;
+  [[maybe_unused]] volatile uint32_t* go_word = tmem_slot + 2;  // fused kernel: the adders' go / stop decision
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -436,6 +446,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             phase ^= 1u;
           }
         }
+      }
+      if (!alive && cta_rank == 0) {
+        // (The second CTA of a pair cannot poll these barriers; the cluster barrier of the teardown
+        // holds it until this CTA is past this point.)
+        // Giving up with copies possibly still in flight into this CTA's (and, in a pair, the
+        // peer's) shared memory: only the last kStages loads can be outstanding, and their bytes are
+        // counted on this CTA's full barriers. Let them land, within a limit, before the teardown
+        // lets any CTA of the cluster leave. Stages below `stage` were armed in the current pass
+        // over the ring, the others in the pass before (a barrier never armed reads as complete).
+        const uint64_t deadline = ptx::global_timer_ns() + kDrainLimitNs;
+        for (uint32_t s = 0; s < static_cast<uint32_t>(kStages); ++s)
+          if (!ptx::mbar_wait_until(full_bar(static_cast<int>(s)), s < stage ? phase : phase ^ 1u, deadline)) break;
       }
     }
     __syncwarp();
@@ -666,7 +688,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------ adders (fused kernel only)
     if constexpr (F::kOn) {
       ptx::setmaxnreg_inc<136>();
-      run_adders<F>(fz, abort_word, static_cast<int>(threadIdx.x) - 32 * (kEpiWarp0 + EPI_WARPS));
+      run_adders<F>(fz, abort_word, go_word, static_cast<int>(threadIdx.x) - 32 * (kEpiWarp0 + EPI_WARPS));
     }
   }
 

@@ -127,6 +127,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return mbar_wait_limit<kClusterScope, kBackoffNs>(bar, parity, abort_word, who, kWaitLimitNs);
 }
 
+// Waits for a phase without the abort protocol, until `deadline_ns` of the global timer at the
+// latest: what a CTA that is already giving up uses to let its own copies in flight land.
+__device__ __forceinline__ bool mbar_wait_until(uint32_t bar, uint32_t parity, uint64_t deadline_ns) {
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() > deadline_ns) return false;
+    __nanosleep(64);
+  }
+}
+
 // ---- register reallocation between warpgroups --------------------------------------------------
 // All four warps of a warpgroup execute these together. A kernel launched with R registers per
 // thread may hand registers of its light warpgroups (dec) to its heavy ones (inc); the sum over the
