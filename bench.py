@@ -10,17 +10,20 @@ table picks them, bf16 operands, fp32 accumulation and aggregation, bf16 result)
   quoted on), algorithm classic / depth 2, schedule from the library's tuner table. ``value`` times
   K steps with the inputs resident in HBM; ``e2e`` times the same product through
   ``fixed_strassen_fp32_agg.strassen_matmul_n_layers`` with pinned host buffers and all three copies
-  inside the timed region. ``interleaved`` is the comparison with cuBLAS dense on the same GPU: the
-  two arms alternate (A B A B ...), every turn starts on a rested GPU and runs back to back for
+  inside the timed region. ``interleaved`` is the comparison with cuBLAS dense on the same GPU: three
+  arms (separate passes, fused kernel, cuBLAS) take turns, every turn starts on a rested GPU and runs back to back for
   ``--seconds``; the first 20 calls of a turn are its "burst" figure, the last second its "sustained"
   one, each with the SM clock sampled during the turn. ``reference_gpu`` is the reference recursion
   (the oracle port) on CUDA tensors, i.e. the reference as it would run on this GPU with cuBLAS
   sub-products. ``stages_ms`` comes from the library's own stage events recorded during the K timed
   steps.
 * N > 1 (launched by torch.distributed.run, one rank per GPU): M = N = K = 32768, A split into row
-  blocks, B replicated; every rank runs the algorithm the tuner table picks for its block and stores
-  every finished tile into all ranks' C over NVLink from the product kernel itself (peer stores; no
-  NCCL collective in the timed path; ``--exchange nccl`` gathers with an NCCL all-gather instead).
+  blocks, B replicated; every rank runs the algorithm the tuner table picks for its block (a dense product at four ranks
+  and more, where replicated operand sums no longer pay) and stores
+  every finished tile into all ranks' C over NVLink from the product kernel itself (one NVLS multicast
+  store per 16 bytes where the switch offers it and the block is a dense product, else one ordinary
+  store per peer; no NCCL collective in the timed path; ``--exchange nccl`` gathers with an NCCL
+  all-gather instead).
   Total work is fixed: scaling "strong". After the timed region every rank recomputes row panels that
   other ranks own and compares them bit for bit with what arrived (``verify``); a mismatch ends the
   run with a non-zero exit code. Then a GPT-2-124M FSDP train step with every Linear through the
@@ -228,7 +231,7 @@ def workload_config(n_gpus):
                 "l2": "inputs (1.6 GB) exceed L2 (126 MB); no flush between steps"}
     return {"workload": f"row-sharded product, M=N=K=32768, bf16 inputs N(0,1)/sqrt(K), A in {n_gpus} row "
                         "blocks, B replicated, every rank ends with the whole C (the multi-GPU configuration); "
-                        "per-rank algorithm from the tuner table",
+                        "per-rank algorithm from the tuner table (dense at 4 ranks and more)",
             "M": 32768, "N": 32768, "K": 32768, "parallelism": f"rowshard{n_gpus}",
             "l2": "inputs exceed L2 (126 MB); no flush between steps"}
 
@@ -583,7 +586,8 @@ def run_gpu_arm(args):
             line["config"]["panels"] = plan.panels if plan is not None else args.panels
             if plan is not None:
                 line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
-                                              "shape": [plan.prow, n, n], "from": "tuner table" if args.algo == "auto" else "flag"}
+                                              "shape": [plan.prow, n, n], "from": ("flag" if args.algo != "auto" else
+                                                       "plan rule: dense at 4 ranks and more" if world >= 4 else "tuner table")}
             calls = max(stages["calls"], 1) / args.steps     # panels per step
             line["stages_ms"] = {"B_operand_blocks": round(st["operand_blocks_B"] * calls, 4),
                                  "A_operand_blocks": round(st["operand_blocks_A"] * calls, 4),
@@ -722,7 +726,7 @@ def main():
                     help="N = 1: schedule of the Strassen passes ('auto' = the library's tuner table)")
     ap.add_argument("--panels", type=int, default=1, help="row panels per rank (N > 1)")
     ap.add_argument("--algo", default="auto", choices=["auto", "dense", "classic", "winograd"],
-                    help="N > 1: per-rank algorithm ('auto' = the library's tuner table)")
+                    help="N > 1: per-rank algorithm ('auto' = the library's tuner table; dense at 4 ranks and more)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_push", "peer_copy", "nccl"],
                     help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink (NVLS multicast "
                          "stores for dense blocks where available, plain peer stores otherwise); 'nccl' = all-gather of "
