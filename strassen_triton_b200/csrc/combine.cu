@@ -1,9 +1,10 @@
 // Recombination pass of the Strassen pipeline.
 //
-// Each thread reads one 16-byte position of all 7^depth product blocks, accumulates the
-// 4^depth signed output sums in fp32 registers (all levels at once) and writes, or adds into,
-// the 4^depth blocks of C, rounding once to the output dtype. Every product element is read
-// exactly once and every element of C written exactly once; accesses are 128-bit and coalesced.
+// Each thread reads one position (a 16-byte vector; a pair of 16-bit products in the two-level
+// pass) of all 7^depth product blocks, accumulates the 4^depth signed output sums in fp32
+// registers (all levels at once) and writes, or adds into, the 4^depth blocks of C, rounding once
+// to the output dtype. Every product element is read exactly once and every element of C written
+// exactly once; a warp's accesses are contiguous.
 //
 // It carries the post-additions and the quadrant assembly of the reference:
 // fixed_strassen_fp32_agg.py:47-56 and :115-123 (products widened to fp32, summed, rounded to
@@ -28,7 +29,7 @@ using namespace comb;
 struct CombineKernelParams {
   const void* products;
   void* C;
-  int64_t Mb, nb_vec;  // block rows, 16-byte product vectors per block row
+  int64_t Mb, nb_vec;  // block rows, positions (Combine::VEC elements each) per block row
   int64_t ldc, strideC;
   int32_t out_dtype, beta, vec_ok;
   const void* bias;
@@ -41,7 +42,7 @@ __device__ __forceinline__ float bias_at(const void* bias, int out_dtype, int64_
 }
 
 template <int DEPTH, int ALGO, typename TP>
-__global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 3) combine_kernel(const CombineKernelParams p) {
+__global__ void __launch_bounds__(256, DEPTH == 2 && sizeof(TP) == 4 ? 2 : 3) combine_kernel(const CombineKernelParams p) {
   using CB = Combine<DEPTH, ALGO, TP>;
   constexpr int NQ = CB::NQ, NP = CB::NP, VEC = CB::VEC;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -134,7 +135,7 @@ struct CombinePeersParams {
 };
 
 template <int DEPTH, int ALGO, typename TP>
-__global__ void __launch_bounds__(256, DEPTH == 2 ? 2 : 3) combine_peers_kernel(const CombinePeersParams p) {
+__global__ void __launch_bounds__(256, DEPTH == 2 && sizeof(TP) == 4 ? 2 : 3) combine_peers_kernel(const CombinePeersParams p) {
   using CB = Combine<DEPTH, ALGO, TP>;
   constexpr int NQ = CB::NQ, NP = CB::NP, VEC = CB::VEC;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;

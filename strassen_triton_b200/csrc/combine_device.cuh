@@ -25,22 +25,13 @@ struct PVec {
   static constexpr int N = 16 / sizeof(T);
 };
 
-// 8-byte loads of four 16-bit products: the depth-2 single-pass kernel keeps 16 x 4 accumulators
-// instead of 16 x 8, which triples the resident threads and with them the loads in flight.
-__device__ __forceinline__ void load_pvec4(const __nv_bfloat16* ptr, float (&f)[4]) {
-  const uint2 v = __ldcs(reinterpret_cast<const uint2*>(ptr));
-  f[0] = __uint_as_float(v.x << 16), f[1] = __uint_as_float(v.x & 0xffff0000u);
-  f[2] = __uint_as_float(v.y << 16), f[3] = __uint_as_float(v.y & 0xffff0000u);
+// Two 16-bit products packed in one 32-bit word, widened to fp32.
+__device__ __forceinline__ void unpack_pair(uint32_t w, const __nv_bfloat16*, float (&f)[2]) {
+  f[0] = __uint_as_float(w << 16), f[1] = __uint_as_float(w & 0xffff0000u);
 }
-__device__ __forceinline__ void load_pvec4(const __half* ptr, float (&f)[4]) {
-  const uint2 v = __ldcs(reinterpret_cast<const uint2*>(ptr));
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-  f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
-}
-__device__ __forceinline__ void load_pvec4(const float* ptr, float (&f)[4]) {
-  const float4 v = __ldcs(reinterpret_cast<const float4*>(ptr));
-  f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+__device__ __forceinline__ void unpack_pair(uint32_t w, const __half*, float (&f)[2]) {
+  const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  f[0] = v.x, f[1] = v.y;
 }
 
 // 16 bytes of products widened to fp32; read once.
@@ -92,6 +83,24 @@ __device__ __forceinline__ void store_out(OutT* dst, const float (&f)[N], bool b
       return;
     }
   }
+  if constexpr (N * sizeof(OutT) == 4) {
+    if (vec_ok) {
+      union {
+        uint32_t u;
+        OutT e[N];
+      } pack;
+      if (beta) {
+        pack.u = *reinterpret_cast<const uint32_t*>(dst);
+#pragma unroll
+        for (int i = 0; i < N; ++i) pack.e[i] = cvt<OutT>(widen(pack.e[i]) + f[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) pack.e[i] = cvt<OutT>(f[i]);
+      }
+      *reinterpret_cast<uint32_t*>(dst) = pack.u;
+      return;
+    }
+  }
   if constexpr (N * sizeof(OutT) == 8) {
     if (vec_ok) {
       union {
@@ -114,11 +123,18 @@ __device__ __forceinline__ void store_out(OutT* dst, const float (&f)[N], bool b
   for (int i = 0; i < N; ++i) dst[i] = cvt<OutT>(beta ? widen(dst[i]) + f[i] : f[i]);
 }
 
+// A position is one 16-byte vector of products, except in the two-level single pass over 16-bit
+// products, where it is one pair (4 bytes): 16 x 2 accumulators and 49 words of products then fit
+// some 75 registers, so all 49 loads of a thread are issued before its first addition and three
+// blocks of 256 threads are resident per SM. With wider positions the accumulators crowd the loads
+// out of the register file, they go out in batches, and the pass is bound by memory latency
+// (measured at 16384^2: 0.36 ms against 0.47 ms with 8-byte positions, 0.62 ms with 16-byte ones).
 template <int DEPTH, int ALGO, typename TP>
 struct Combine {
   static constexpr int NQ = sched::ipow(4, DEPTH);
   static constexpr int NP = sched::ipow(7, DEPTH);
-  static constexpr int VEC = DEPTH == 2 ? 4 : PVec<TP>::N;
+  static constexpr bool kPairs = DEPTH == 2 && sizeof(TP) == 2;
+  static constexpr int VEC = kPairs ? 2 : PVec<TP>::N;
 
   template <int P, int R>
   static __device__ __forceinline__ void add_term(const float (&x)[VEC], float (&acc)[NQ][VEC]) {
@@ -133,17 +149,28 @@ struct Combine {
   static __device__ __forceinline__ void one_product(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
                                                      const A& access, std::integer_sequence<int, Rs...>) {
     float x[VEC];
-    if constexpr (VEC == PVec<TP>::N)
-      load_pvec<TP>(prod0 + P * blk_elems, x, access);
-    else
-      load_pvec4(prod0 + P * blk_elems, x);
+    load_pvec<TP>(prod0 + P * blk_elems, x, access);
+    (add_term<P, Rs>(x, acc), ...);
+  }
+
+  template <int P, int... Rs>
+  static __device__ __forceinline__ void one_pair(uint32_t raw, float (&acc)[NQ][VEC], std::integer_sequence<int, Rs...>) {
+    float x[VEC];
+    unpack_pair(raw, static_cast<const TP*>(nullptr), x);
     (add_term<P, Rs>(x, acc), ...);
   }
 
   template <class A = mem::Plain, int... Ps>
   static __device__ __forceinline__ void all_products(const TP* prod0, int64_t blk_elems, float (&acc)[NQ][VEC],
                                                       std::integer_sequence<int, Ps...>, const A& access = A{}) {
-    (one_product<Ps>(prod0, blk_elems, acc, access, std::make_integer_sequence<int, NQ>{}), ...);
+    if constexpr (kPairs) {
+      // every load first (read once: streaming), then the additions in table order
+      uint32_t raw[NP];
+      ((raw[Ps] = __ldcs(reinterpret_cast<const uint32_t*>(prod0 + Ps * blk_elems))), ...);
+      (one_pair<Ps>(raw[Ps], acc, std::make_integer_sequence<int, NQ>{}), ...);
+    } else {
+      (one_product<Ps>(prod0, blk_elems, acc, access, std::make_integer_sequence<int, NQ>{}), ...);
+    }
   }
 };
 
