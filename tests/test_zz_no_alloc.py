@@ -66,3 +66,58 @@ def test_static_scratch_rejects_what_does_not_fit(built_library):
     assert "capacity" in _lib.status_string(rc)
     assert lib.b200s_launch_count() == launches
     assert lib.b200s_matmul_static(None, A.data_ptr(), A.data_ptr(), C.data_ptr(), None) == _lib.ERR_NULL_POINTER
+
+
+CHILD = r"""
+import ctypes, sys, torch
+sys.path.insert(0, %r)
+from strassen_triton_b200 import _lib, ops
+lib = _lib.load()
+dev = torch.device("cuda")
+stream = torch.cuda.current_stream().cuda_stream
+g = torch.Generator(device="cuda").manual_seed(7)
+M, N, K = 512, 768, 1024
+A = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).bfloat16()
+B = (torch.rand(K, N, device=dev, generator=g) * 2 - 1).bfloat16()
+A2 = (torch.rand(M, K, device=dev, generator=g) * 2 - 1).bfloat16()
+C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+C2 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+p, a, b = ops.make_problem(A, B, C, "classic", 2)
+# the very first product of this process goes through the static entry: nothing of the ordinary
+# path (workspace, status words, tuner) has been set up for it
+assert lib.b200s_matmul_static(ctypes.byref(p), a.data_ptr(), b.data_ptr(), C.data_ptr(), stream) == 0
+st, detail = ctypes.c_int32(-1), ctypes.c_int32(-1)
+assert lib.b200s_static_status(stream, ctypes.byref(st), ctypes.byref(detail)) == 0
+torch.cuda.synchronize()          # the first call loaded the kernels and with them the scratch array
+free0, _ = torch.cuda.mem_get_info()
+held0 = torch.cuda.memory_reserved()
+for _ in range(3):
+    assert lib.b200s_matmul_static(ctypes.byref(p), A2.data_ptr(), b.data_ptr(), C2.data_ptr(), stream) == 0
+assert lib.b200s_static_status(stream, ctypes.byref(st), ctypes.byref(detail)) == 0
+torch.cuda.synchronize()
+free1, _ = torch.cuda.mem_get_info()
+assert (st.value, detail.value) == (0, 0), (st.value, detail.value)
+assert free1 == free0, (free0, free1)                     # the driver handed out no device memory
+assert torch.cuda.memory_reserved() == held0
+want = ops.matmul(A, B, algo="classic", depth=2, pipeline=2)
+want2 = ops.matmul(A2, B, algo="classic", depth=2, pipeline=2)
+assert torch.equal(C, want) and torch.equal(C2, want2)
+print("static ok", free0)
+"""
+
+
+def test_static_entry_first_in_a_fresh_process_takes_no_device_memory(built_library):
+    """In a process of its own the static entry is the first thing the library does; once the first
+    call has loaded the kernels, further calls leave the device's free memory exactly as it was."""
+    import os
+    import subprocess
+    import sys
+
+    if not torch.cuda.is_available():
+        pytest.fail("this test needs a CUDA device")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TORCHDYNAMO_DISABLE="1")
+    out = subprocess.run([sys.executable, "-c", CHILD % root], cwd=root, env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    assert "static ok" in out.stdout
