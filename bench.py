@@ -8,9 +8,10 @@ table picks them, bf16 operands, fp32 accumulation and aggregation, bf16 result)
 
 * N = 1: M = N = K = 16384, inputs U(-1,1) from seed 0 (the configuration the headline metric is
   quoted on), algorithm classic / depth 2, schedule from the library's tuner table. ``value`` times
-  K steps with the inputs resident in HBM; ``e2e`` times the same product through
-  ``fixed_strassen_fp32_agg.strassen_matmul_n_layers`` with pinned host buffers and all three copies
-  inside the timed region. ``interleaved`` is the comparison with cuBLAS dense on the same GPU: three
+  K steps with the inputs resident in HBM; ``e2e`` times the same product with operands and result in
+  pinned host memory through ``strassen_triton_b200.host.HostStreamedMatmul`` (B, then A in row panels,
+  products and the way back of C overlapping the arrivals; all copies inside the timed region), and
+  reports beside it the plain sequence copy, copy, ``strassen_matmul_n_layers``, copy. ``interleaved`` is the comparison with cuBLAS dense on the same GPU: three
   arms (separate passes, fused kernel, cuBLAS) take turns, every turn starts on a rested GPU and runs back to back for
   ``--seconds``; the first 20 calls of a turn are its "burst" figure, the last second its "sustained"
   one, each with the SM clock sampled during the turn. ``reference_gpu`` is the reference recursion
@@ -60,6 +61,8 @@ UNIT = "TFLOP/s"
 # one-kernel ncu capture of 14 products of 4096^3; a full launch of the N = 1 workload runs 49 such
 # products and its traffic grows in proportion.
 GEMM_DRAM_BYTES_14_PRODUCTS = 1.334e9 + 0.447e9
+E2E_PANELS = 8   # row panels of A in the end-to-end leg (host-resident operands streamed over PCIe)
+
 GEMM_DRAM_SOURCE = ("ncu one-kernel capture, 14 products of 4096^3 (1.334 GB read + 0.447 GB written), "
                     "scaled by 49/14 to the 49 products of a launch")
 
@@ -525,14 +528,24 @@ def run_gpu_arm(args):
     hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True)
     hA.copy_(A)
     hB.copy_(B)
+    e2e_sequential = None
     if world == 1:
+        from strassen_triton_b200.host import HostStreamedMatmul
+
         hC = torch.empty((n, n), dtype=torch.bfloat16, pin_memory=True)
 
-        def e2e_step():
+        def sequential_step():      # copy A, copy B, multiply, copy C, one after the other
             dA = hA.to(dev, non_blocking=True)
             dB = hB.to(dev, non_blocking=True)
             out = api.strassen_matmul_n_layers(dA, dB, depth, torch.bfloat16)
             hC.copy_(out, non_blocking=True)
+
+        sequential_step()
+        e2e_sequential = flops * 3 / (timed(sequential_step, 3, sync, barrier) * 1e-3) / 1e12
+        streamed = HostStreamedMatmul(n, n, n, torch.bfloat16, algo="classic", depth=depth, panels=E2E_PANELS)
+
+        def e2e_step():             # B, then A in row panels; products and C's way back overlap the arrivals
+            streamed(hA, hB, hC)
     else:
         r0, r1 = row_block(n, world, rank)
         hC = torch.empty((r1 - r0, n), dtype=torch.bfloat16, pin_memory=True)
@@ -567,11 +580,18 @@ def run_gpu_arm(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world), "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "api": "fixed_strassen_fp32_agg.strassen_matmul_n_layers" if world == 1
+                    "steps": e2e_steps, "api": "strassen_triton_b200.host.HostStreamedMatmul" if world == 1
                     else ("strassen_triton_b200.sharded.PeerShardedMatmul" if plan is not None
                           else "strassen_triton_b200.sharded.sharded_matmul")},
             "gpu_launches": int(launches),
         }
+        if e2e_sequential is not None:
+            line["e2e"]["how"] = (f"pinned host operands streamed over PCIe: B, then A in {E2E_PANELS} row panels; each panel "
+                                  "is multiplied (two levels, B's operand blocks reused) as it arrives and its rows of C go "
+                                  "back while the next panel is multiplied")
+            line["e2e"]["sequential_value"] = round(e2e_sequential, 2)
+            line["e2e"]["sequential_api"] = ("fixed_strassen_fp32_agg.strassen_matmul_n_layers between plain copies "
+                                             "(copy A, copy B, multiply, copy C, one after the other)")
     stage_names = ("operand_blocks_A", "operand_blocks_B", "products", "recombination")
 
     if world > 1:
