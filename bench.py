@@ -61,7 +61,7 @@ UNIT = "TFLOP/s"
 # one-kernel ncu capture of 14 products of 4096^3; a full launch of the N = 1 workload runs 49 such
 # products and its traffic grows in proportion.
 GEMM_DRAM_BYTES_14_PRODUCTS = 1.334e9 + 0.447e9
-E2E_PANELS = 8   # row panels of A in the end-to-end leg (host-resident operands streamed over PCIe)
+E2E_PANELS = 16  # row panels of A in the end-to-end leg (host-resident operands streamed over PCIe)
 
 GEMM_DRAM_SOURCE = ("ncu one-kernel capture, 14 products of 4096^3 (1.334 GB read + 0.447 GB written), "
                     "scaled by 49/14 to the 49 products of a launch")
