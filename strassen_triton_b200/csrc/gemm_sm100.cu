@@ -52,6 +52,8 @@ struct GemmKernelParams {
   uint8_t* dst[8];            // their (0,0) elements; copy 0 is stored by TMA, the others by ordinary stores
   const void* bias;           // optional row vector (N elements of out_dtype) added before the rounding
   uint8_t* mc;                // or: one NVLS multicast address that reaches every GPU's copy (then n_dst == 2)
+  int32_t stagger;            // 1: clusters hold their remote stores back by different shares of the tile period
+                              // (per-peer stores at 4 GPUs, 32768^3: 15.0 -> 14.4 ms a step; no gain with multicast)
   int64_t ldc, strideC;
   void* C;
   uint32_t* status;
@@ -534,6 +536,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint64_t store_policy = ptx::make_evict_first_policy();
     int it = 0;
     int stage_flip = 0;
+    // Several destinations: the tiles of a wave finish together, and with them come the remote stores
+    // of all CTAs of all GPUs in one burst. The epilogue is not needed again before the next tile is
+    // done, so every cluster holds its stores back by its own share of the tile period it observed
+    // last: the bursts become a steady stream.
+    uint32_t tile_seen_ns = 0, hold_ns = 0;
     for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it) {
       int b, mt, nt;
       decode_tile(p, tile, b, mt, nt);
@@ -544,6 +551,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) ok = ptx::mbar_wait<kCtaGroup == 2, 64>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
+      if (p.n_dst > 1 && p.stagger) {
+        const uint32_t now = static_cast<uint32_t>(ptx::global_timer_ns());  // differences survive the wrap
+        if (it > 0) {
+          const uint32_t period = now - tile_seen_ns;
+          // clusters 0 .. n-1 spread over 60 % of the period; nothing for periods under 20 us or over 50 ms
+          hold_ns = (period > 20000u && period < 50000000u)
+                        ? (period / 10u * 6u) * static_cast<uint32_t>(cluster_id) / static_cast<uint32_t>(num_clusters)
+                        : 0u;   // at most 3e7 x 73: fits 32 bits
+        }
+        tile_seen_ns = now;
+      }
       ptx::tc_fence_after_sync();
       const int row_warp = mt * (kBM * kCtaGroup) + static_cast<int>(cta_rank) * kBM + lane_group * 32;
       const int row = row_warp + lane;
@@ -633,6 +651,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (c + 1 < kChunks) ptx::tmem_ld_32x32(taddr + (c + 1) * 32, r);
         }
         release_accumulator();
+        if (hold_ns != 0) {
+          // bounded by construction: at most 60 % of a period of at most 50 ms, in short sleeps
+          const uint32_t t0 = static_cast<uint32_t>(ptx::global_timer_ns());
+          while (static_cast<uint32_t>(ptx::global_timer_ns()) - t0 < hold_ns) __nanosleep(1000);
+        }
 #pragma unroll
         for (int g = 0; g < kChunks / 2; ++g) {
           uint32_t h[32];
@@ -915,6 +938,7 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   kp.bias = g.bias;
   kp.tma_store = tma_store ? 1 : 0;
   kp.n_dst = kp.mc ? 2 : n_dst;
+  kp.stagger = (kp.n_dst > 1 && kp.mc == nullptr) ? 1 : 0;  // measured: helps per-peer stores, nothing for multicast
   kp.M = static_cast<int32_t>(g.M);
   kp.N = static_cast<int32_t>(g.N);
   const int tile_m = kBM * cta_group;
