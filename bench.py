@@ -483,7 +483,8 @@ def run_gpu_arm(args):
             plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
                                      panels=args.panels, device=dev,
                                      exchange={"peer": "auto", "peer_store": "store", "peer_multicast": "multicast",
-                                               "peer_push": "push", "peer_copy": "copy"}[args.exchange])
+                                               "peer_push": "push", "peer_copy": "copy", "peer_overlap": "overlap"}[args.exchange],
+                                     push_sms=args.push_sms)
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
         else:
@@ -602,7 +603,10 @@ def run_gpu_arm(args):
             per_step = ms / args.steps
             line["config"]["exchange"] = (f"{plan.exchange}: stores from the product kernel into every rank's C (no "
                                           "collective in the timed path)" if plan is not None and plan.exchange in
-                                          ("store", "multicast") else args.exchange)
+                                          ("store", "multicast") else
+                                          f"overlap: row panel i is sent by a kernel on {plan.push_sms} SMs while panel i+1 is "
+                                          "multiplied on the others (no collective in the timed path)"
+                                          if plan is not None and plan.exchange == "overlap" else args.exchange)
             line["config"]["panels"] = plan.panels if plan is not None else args.panels
             if plan is not None:
                 line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
@@ -747,10 +751,12 @@ def main():
     ap.add_argument("--panels", type=int, default=1, help="row panels per rank (N > 1)")
     ap.add_argument("--algo", default="auto", choices=["auto", "dense", "classic", "winograd"],
                     help="N > 1: per-rank algorithm ('auto' = the library's tuner table; dense at 4 ranks and more)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_push", "peer_copy", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_overlap", "peer_push", "peer_copy", "nccl"],
                     help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink (NVLS multicast "
                          "stores for dense blocks where available, plain peer stores otherwise); 'nccl' = all-gather of "
                          "the row blocks")
+    ap.add_argument("--push-sms", type=int, default=8, help="N > 1, --exchange peer_overlap: SMs left to the kernel that sends "
+                                                            "a finished row panel while the next one is multiplied")
     ap.add_argument("--fsdp", type=int, default=1, help="N > 1: also time the FSDP GPT-2 step (0 = skip)")
     ap.add_argument("--quick", action="store_true", help="N = 1: skip the comparison arms (for a launch list under ncu)")
     ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, cublas_grouped, "

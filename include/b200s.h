@@ -313,6 +313,20 @@ int b200s_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, u
  */
 int b200s_push_rows(const void* src_device, void* const* dst_list, int n_dst, size_t bytes, void* stream);
 
+/*
+ * Exchange beside the products. b200s_set_product_sms(n) makes every product kernel launched
+ * afterwards by this process occupy at most n SMs (0 = all; returns the previous setting), which
+ * leaves the others to kernels of other streams. b200s_push_panel copies `bytes` (a multiple of 16,
+ * both ends 16-byte aligned) of finished rows with at most max_blocks blocks of 512 threads: to the
+ * n_dst (1..8) peer copies in dst_list, or, when mc_dst is given, once to that NVLS multicast address
+ * of the same rows (the NVSwitch writes every GPU's copy; dst_list and n_dst are ignored). A
+ * row-sharded product computes row panel i+1 on most SMs while a few SMs send panel i. No counterpart
+ * in the reference (it has no multi-GPU product).
+ */
+int b200s_set_product_sms(int n);
+int b200s_push_panel(const void* src_device, void* const* dst_list, int n_dst, void* mc_dst, size_t bytes,
+                     int max_blocks, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

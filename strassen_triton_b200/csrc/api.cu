@@ -529,6 +529,13 @@ int sm_count() {
   return (s && s->ok) ? s->sms : 0;
 }
 
+static std::atomic<int> g_product_sms{0};   // 0 = no limit
+int product_sm_count() {
+  const int all = sm_count();
+  const int lim = g_product_sms.load(std::memory_order_relaxed);
+  return (lim > 0 && lim < all) ? lim : all;
+}
+
 }  // namespace b200s
 
 using namespace b200s;
@@ -658,6 +665,17 @@ int b200s_combine_peers(const b200s_problem* p, const void* products, void* cons
   c.beta = 0;
   if (!device_status_words()) return B200S_ERR_NO_DEVICE;
   return launch_combine_peers(c, C_list, n_dst, static_cast<cudaStream_t>(stream));
+}
+
+int b200s_set_product_sms(int n) {
+  if (n < 0) return B200S_ERR_BAD_SHAPE;
+  if (n == 1) n = 2;                         // a CTA pair needs two
+  return g_product_sms.exchange(n & ~1, std::memory_order_relaxed);
+}
+
+int b200s_push_panel(const void* src, void* const* dst_list, int n_dst, void* mc_dst, size_t bytes, int max_blocks,
+                     void* stream) {
+  return launch_push_panel(src, dst_list, n_dst, mc_dst, bytes, max_blocks, static_cast<cudaStream_t>(stream));
 }
 
 int b200s_push_rows(const void* src, void* const* dst_list, int n_dst, size_t bytes, void* stream) {

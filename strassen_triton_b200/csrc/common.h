@@ -15,6 +15,8 @@ void count_launch(int n = 1);
 // Device status words (2 x uint32) of the current device, allocated on first use. nullptr on failure.
 uint32_t* device_status_words();
 int sm_count();
+// SMs the product kernels may occupy: sm_count() unless b200s_set_product_sms lowered it.
+int product_sm_count();
 
 #define B200S_CUDA_OK(expr)                          \
   do {                                               \
@@ -123,6 +125,10 @@ int launch_peer_barrier(void* const* pads, int rank, int world, uint32_t epoch, 
                         cudaStream_t stream);
 // Contiguous copy of `bytes` (a multiple of 16) from src to n_dst (<= 8) destinations, small SM footprint.
 int launch_push_rows(const void* src, void* const* dst, int n_dst, size_t bytes, cudaStream_t stream);
+// The same copy by at most max_blocks blocks of 512 threads, to n_dst peer copies or, when mc_dst is
+// given, once to a multicast address (peer.cu).
+int launch_push_panel(const void* src, void* const* dst, int n_dst, void* mc_dst, size_t bytes, int max_blocks,
+                      cudaStream_t stream);
 
 
 // Outer-group forms used by the pipelined driver (api.cu): operand blocks of a few outer products,

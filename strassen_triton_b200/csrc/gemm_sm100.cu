@@ -878,7 +878,7 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
 
   uint32_t* status = g.status ? g.status : device_status_words();
   if (!status) return B200S_ERR_CUDA;
-  const int sms = g.sms > 0 ? g.sms : sm_count();
+  const int sms = g.sms > 0 ? g.sms : product_sm_count();
   if (sms < 2) return B200S_ERR_NO_DEVICE;
 
   // Tile variant: 1 = one CTA, 128 x 256 tiles; 2 = CTA pair, 256 x 256 tiles, double-buffered

@@ -157,7 +157,8 @@ class PeerShardedMatmul:
     """
 
     def __init__(self, M: int, N: int, K: int, dtype=torch.bfloat16, group=None, algo: str = "auto",
-                 depth: int = -1, panels: int = 1, device=None, exchange: str = "auto", barrier_ms: float = 2000.0):
+                 depth: int = -1, panels: int = 1, device=None, exchange: str = "auto", barrier_ms: float = 2000.0,
+                 push_sms: int = 8):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -172,8 +173,10 @@ class PeerShardedMatmul:
             raise ValueError("at most 8 ranks (one node)")
         if M % self.world:
             raise ValueError("M must be a multiple of the number of ranks")
-        if exchange not in ("auto", "store", "multicast", "copy", "push"):
-            raise ValueError("exchange must be 'auto', 'store', 'multicast', 'push' or 'copy'")
+        if exchange not in ("auto", "store", "multicast", "copy", "push", "overlap"):
+            raise ValueError("exchange must be 'auto', 'store', 'multicast', 'overlap', 'push' or 'copy'")
+        if exchange == "overlap" and panels < 2:
+            panels = 4                       # the last panel's transfer is the part that is not hidden
         self.M, self.N, self.K, self.dtype = M, N, K, dtype
         self.exchange = exchange
         self.rows = M // self.world
@@ -232,6 +235,8 @@ class PeerShardedMatmul:
         self._es = self.C.element_size()
         self._ws = None
         self.copy_streams = [torch.cuda.Stream(self.device) for _ in range(self.world)] if exchange == "copy" else []
+        self.push_stream = torch.cuda.Stream(self.device, priority=-1) if exchange == "overlap" else None
+        self.push_sms = push_sms
         self.ev_panel = [torch.cuda.Event() for _ in range(panels)]
 
     def _barrier(self, stream):
@@ -243,6 +248,54 @@ class PeerShardedMatmul:
         """The product of one row panel as this plan computes it, into fresh local memory: the same
         kernels and arithmetic as the exchanged panel, for checking what arrived bit for bit."""
         return self._ops.matmul(a_panel, B, algo=self.algo, depth=self.depth, pipeline=2, fuse=2)
+
+    def _overlapped(self, A_block: torch.Tensor, B: torch.Tensor, stream) -> torch.Tensor:
+        """Row panels one after the other into this rank's own rows of C, each on all SMs but
+        ``push_sms``; as soon as a panel is done a small kernel on the push stream sends its rows to
+        every rank (one multicast store per 16 bytes where the switch offers it, else one store per
+        peer) on the SMs the next panel's product leaves free. Only the last panel's transfer is not
+        hidden behind a product."""
+        import ctypes
+
+        lib, ops = self._lib.load(), self._ops
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        before = lib.b200s_set_product_sms(max(2, sms - self.push_sms))
+        try:
+            for i in range(self.panels):
+                p0 = i * self.prow
+                row0 = self.rank * self.rows + p0
+                c_rows = self.C[row0: row0 + self.prow]
+                prob, a2, b2 = ops.make_problem(A_block[p0:p0 + self.prow], B, c_rows, self.algo, self.depth, pipeline=2,
+                                                fuse=2, b_blocks_ready=i > 0 and self.depth > 0)
+                need = ops.workspace_bytes(prob)
+                if need and (self._ws is None or self._ws.numel() < need):
+                    if i > 0:
+                        raise RuntimeError("scratch of a later panel larger than the first panel's")
+                    self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+                self._lib.check(lib.b200s_matmul(ctypes.byref(prob), a2.data_ptr(), b2.data_ptr(), c_rows.data_ptr(),
+                                                 self._ws.data_ptr() if need else None, need, stream.cuda_stream))
+                if self.world == 1:
+                    continue
+                self.ev_panel[i].record(stream)
+                self.push_stream.wait_event(self.ev_panel[i])
+                offset = row0 * self.N * self._es
+                nbytes = self.prow * self.N * self._es
+                blocks = self.push_sms if i + 1 < self.panels else sms     # nothing runs beside the last transfer
+                if self.multicast_ptr:
+                    rc = lib.b200s_push_panel(c_rows.data_ptr(), None, 0, self.multicast_ptr + offset, nbytes,
+                                              blocks, self.push_stream.cuda_stream)
+                else:
+                    peers = [self.peer_ptrs[(self.rank + k) % self.world] + offset for k in range(1, self.world)]
+                    dst = (ctypes.c_void_p * len(peers))(*peers)
+                    rc = lib.b200s_push_panel(c_rows.data_ptr(), dst, len(peers), None, nbytes, blocks,
+                                              self.push_stream.cuda_stream)
+                self._lib.check(rc)
+        finally:
+            lib.b200s_set_product_sms(before)
+        if self.push_stream is not None:
+            stream.wait_stream(self.push_stream)
+        self._barrier(stream)                # every rank's rows have been sent and have landed
+        return self.C
 
     def check(self) -> None:
         """Synchronises and raises if a device-side wait (a barrier, a kernel role) gave up."""
@@ -258,6 +311,8 @@ class PeerShardedMatmul:
             raise ValueError("operand shapes do not match the plan")
         stream = torch.cuda.current_stream(self.device)
         self._barrier(stream)                # every rank is done with the previous contents of C
+        if self.exchange == "overlap":
+            return self._overlapped(A_block, B, stream)
         for i in range(self.panels):
             p0 = i * self.prow
             a_panel = A_block[p0:p0 + self.prow]

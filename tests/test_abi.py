@@ -205,6 +205,14 @@ def test_new_entry_points_validate_before_touching_a_device(lib):
     assert lib.b200s_profile_begin(0) == _lib.ERR_BAD_SHAPE
     assert lib.b200s_profile_end(None, None) == _lib.ERR_NULL_POINTER
     assert lib.b200s_workspace_bytes(ctypes.byref(problem(fuse=4)), ctypes.byref(ctypes.c_size_t(0))) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_push_panel(None, dst, 2, None, 256, 8, None) == _lib.ERR_NULL_POINTER
+    assert lib.b200s_push_panel(16, None, 0, None, 256, 8, None) == _lib.ERR_NULL_POINTER      # neither peers nor multicast
+    assert lib.b200s_push_panel(16, dst, 2, None, 250, 8, None) == _lib.ERR_BAD_SHAPE         # not whole 16-byte vectors
+    assert lib.b200s_push_panel(16, dst, 2, None, 256, 0, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_push_panel(16, dst, 9, None, 256, 8, None) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_push_panel(24, None, 0, 32, 256, 8, None) == _lib.ERR_BAD_ALIGNMENT
+    assert lib.b200s_set_product_sms(-1) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_set_product_sms(140) == 0 and lib.b200s_set_product_sms(0) == 140        # returns the previous setting
 
 
 def test_fused_schedule_keeps_its_counters_at_the_end_of_the_scratch(lib):

@@ -32,7 +32,7 @@ def single_rank_group(built_library):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["store", "push", "copy"])
+@pytest.mark.parametrize("exchange", ["store", "push", "copy", "overlap"])
 @pytest.mark.parametrize("algo,depth,panels", [("classic", 2, 1), ("classic", 2, 2), ("dense", 0, 2), ("winograd", 1, 1)])
 def test_peer_sharded_plan_single_rank(single_rank_group, exchange, algo, depth, panels):
     from strassen_triton_b200 import ops
@@ -46,6 +46,8 @@ def test_peer_sharded_plan_single_rank(single_rank_group, exchange, algo, depth,
                                  panels=panels, exchange=exchange, barrier_ms=200)
     except RuntimeError as e:  # symmetric memory not available in this environment
         pytest.skip(f"symmetric memory rendezvous unavailable: {e}")
+    if exchange == "overlap" and panels == 1:
+        panels = 4              # the overlapped exchange needs several panels and takes four
     assert (plan.algo, plan.depth, plan.panels, plan.exchange) == (algo, depth, panels, exchange)
     for _ in range(2):
         C = plan(A, B)
