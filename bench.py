@@ -483,7 +483,8 @@ def run_gpu_arm(args):
             plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
                                      panels=args.panels, device=dev,
                                      exchange={"peer": "auto", "peer_store": "store", "peer_multicast": "multicast",
-                                               "peer_push": "push", "peer_copy": "copy", "peer_overlap": "overlap"}[args.exchange],
+                                               "peer_push": "push", "peer_copy": "copy", "peer_overlap": "overlap",
+                                               "peer_senders": "senders"}[args.exchange],
                                      push_sms=args.push_sms)
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
@@ -607,6 +608,10 @@ def run_gpu_arm(args):
                                           f"overlap: row panel i is sent by a kernel on {plan.push_sms} SMs while panel i+1 is "
                                           "multiplied on the others (no collective in the timed path)"
                                           if plan is not None and plan.exchange == "overlap" else args.exchange)
+            if plan is not None and plan.sender_sms:
+                line["config"]["exchange"] = (f"{plan.exchange} stores by {plan.sender_sms} sending CTAs of the product kernel, "
+                                              "block of columns by block of columns as C gets finished (no collective in the "
+                                              "timed path)")
             line["config"]["panels"] = plan.panels if plan is not None else args.panels
             if plan is not None:
                 line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
@@ -751,7 +756,7 @@ def main():
     ap.add_argument("--panels", type=int, default=1, help="row panels per rank (N > 1)")
     ap.add_argument("--algo", default="auto", choices=["auto", "dense", "classic", "winograd"],
                     help="N > 1: per-rank algorithm ('auto' = the library's tuner table; dense at 4 ranks and more)")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_overlap", "peer_push", "peer_copy", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_store", "peer_multicast", "peer_senders", "peer_overlap", "peer_push", "peer_copy", "nccl"],
                     help="N > 1: 'peer' = the product kernel stores into every rank's C over NVLink (NVLS multicast "
                          "stores for dense blocks where available, plain peer stores otherwise); 'nccl' = all-gather of "
                          "the row blocks")

@@ -324,6 +324,14 @@ int b200s_push_rows(const void* src_device, void* const* dst_list, int n_dst, si
  * in the reference (it has no multi-GPU product).
  */
 int b200s_set_product_sms(int n);
+/*
+ * b200s_set_sender_sms(n): a dense product with several destinations (b200s_matmul_peers,
+ * b200s_matmul_multicast) launched afterwards by this process gives n (even, 0..64; 0 = none; returns
+ * the previous setting) of its CTAs to sending instead of multiplying: they wait until a block of
+ * columns of C is finished, read it from this GPU's copy and store it to the other copies, so the
+ * epilogue warps of the multiplying CTAs store locally only. One kernel, one launch.
+ */
+int b200s_set_sender_sms(int n);
 int b200s_push_panel(const void* src_device, void* const* dst_list, int n_dst, void* mc_dst, size_t bytes,
                      int max_blocks, void* stream);
 

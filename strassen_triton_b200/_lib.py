@@ -102,6 +102,7 @@ SIGNATURES = {
     "b200s_push_rows": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int, ctypes.c_size_t,
                                        ctypes.c_void_p]),
     "b200s_set_product_sms": (ctypes.c_int, [ctypes.c_int]),
+    "b200s_set_sender_sms": (ctypes.c_int, [ctypes.c_int]),
     "b200s_push_panel": (ctypes.c_int, [ctypes.c_void_p, _P(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p,
                                         ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]),
     "b200s_combine": (ctypes.c_int, [_P(Problem), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),

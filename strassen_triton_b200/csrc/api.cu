@@ -68,9 +68,11 @@ DeviceState* current_device_state() {
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return &s;
     if (prop.major != 10) return &s;  // tcgen05 / TMEM kernels: sm_100 only
     s.sms = prop.multiProcessorCount;
+    // two status words, then (64 bytes on) the counters of the sending CTAs
     void* ptr = nullptr;
-    if (cudaMalloc(&ptr, 2 * sizeof(uint32_t)) != cudaSuccess) return &s;
-    if (cudaMemset(ptr, 0, 2 * sizeof(uint32_t)) != cudaSuccess) return &s;
+    const size_t bytes = 64 + sizeof(uint32_t) * kSendUnits;
+    if (cudaMalloc(&ptr, bytes) != cudaSuccess) return &s;
+    if (cudaMemset(ptr, 0, bytes) != cudaSuccess) return &s;
     s.status = static_cast<uint32_t*>(ptr);
     s.ok = true;
   }
@@ -529,6 +531,14 @@ int sm_count() {
   return (s && s->ok) ? s->sms : 0;
 }
 
+uint32_t* device_send_counters() {
+  DeviceState* s = current_device_state();
+  return (s && s->ok) ? s->status + 16 : nullptr;
+}
+
+static std::atomic<int> g_sender_sms{0};    // 0 = the exchange stays in the epilogue
+int sender_sm_count() { return g_sender_sms.load(std::memory_order_relaxed); }
+
 static std::atomic<int> g_product_sms{0};   // 0 = no limit
 int product_sm_count() {
   const int all = sm_count();
@@ -673,6 +683,11 @@ int b200s_set_product_sms(int n) {
   return g_product_sms.exchange(n & ~1, std::memory_order_relaxed);
 }
 
+int b200s_set_sender_sms(int n) {
+  if (n < 0 || n > 64) return B200S_ERR_BAD_SHAPE;
+  return g_sender_sms.exchange(n & ~1, std::memory_order_relaxed);
+}
+
 int b200s_push_panel(const void* src, void* const* dst_list, int n_dst, void* mc_dst, size_t bytes, int max_blocks,
                      void* stream) {
   return launch_push_panel(src, dst_list, n_dst, mc_dst, bytes, max_blocks, static_cast<cudaStream_t>(stream));
@@ -738,6 +753,7 @@ static int run_matmul(const b200s_problem* p_in, const void* A, const void* B, v
   if (plan.depth == 0) {
     g.A = A, g.B = B, g.C = C;
     g.n_dst = n_dst, g.C_list = dst_list, g.mc_dst = mc_dst, g.bias = bias;
+    g.send_sms = (n_dst > 1 || mc_dst) ? sender_sm_count() : 0;
     g.M = p->M, g.N = p->N, g.K = p->K, g.batch = p->batch;
     g.lda = p->lda, g.ldb = p->ldb, g.ldc = p->ldc;
     g.strideA = p->strideA, g.strideB = p->strideB, g.strideC = p->strideC;

@@ -17,6 +17,11 @@ uint32_t* device_status_words();
 int sm_count();
 // SMs the product kernels may occupy: sm_count() unless b200s_set_product_sms lowered it.
 int product_sm_count();
+// Counters (kSendUnits 32-bit words per device) the sending CTAs of a row-sharded product wait on.
+constexpr int kSendUnits = 4000;
+uint32_t* device_send_counters();
+// SMs a product with several destinations gives to sending CTAs (b200s_set_sender_sms; 0 = none).
+int sender_sm_count();
 
 #define B200S_CUDA_OK(expr)                          \
   do {                                               \
@@ -57,6 +62,9 @@ struct GemmArgs {
   // Optional: an NVLS multicast address of C(0,0) that maps to every GPU's copy. C (or C_list[0])
   // is then this GPU's own copy, written by TMA, and every tile is also stored once to mc_dst.
   void* mc_dst = nullptr;
+  // Optional, with several destinations: the last send_sms CTAs of the launch do the remote stores
+  // (block of columns by block of columns, as C gets finished) instead of the epilogue warps.
+  int send_sms = 0;
 };
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 // One-thread kernel that waits `limit_ns` on a barrier nobody signals and reports the give-up in the

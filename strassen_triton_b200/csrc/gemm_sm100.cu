@@ -44,6 +44,7 @@ struct GemmKernelParams {
   int32_t k_blocks;
   int32_t total_tiles;
   int32_t raster_group;       // m-tiles that share a band of n-tiles in the tile order
+  int32_t wave_tiles;         // tiles the whole device works on at a time (its SMs / CTAs per tile)
   int32_t a_mn, b_mn;
   int32_t fmt;                // operand format field of the instruction descriptor
   int32_t out_dtype, beta;
@@ -52,6 +53,9 @@ struct GemmKernelParams {
   uint8_t* dst[8];            // their (0,0) elements; copy 0 is stored by TMA, the others by ordinary stores
   const void* bias;           // optional row vector (N elements of out_dtype) added before the rounding
   uint8_t* mc;                // or: one NVLS multicast address that reaches every GPU's copy (then n_dst == 2)
+  int32_t send_ctas;          // > 0: the last send_ctas CTAs of the grid multiply nothing; they send finished blocks of
+                              // columns of C to dst[1..] / mc while the others multiply (the epilogue then stores locally only)
+  uint32_t* send_counters;    // one counter per (band of m-tiles, n-tile): epilogue warps done with a tile of it
   int32_t stagger;            // 1: clusters hold their remote stores back by different shares of the tile period
                               // (per-peer stores at 4 GPUs, 32768^3: 15.0 -> 14.4 ms a step; no gain with multicast)
   int64_t ldc, strideC;
@@ -67,7 +71,8 @@ enum : uint32_t {
   kWhoEpilogue = 4,
   kWhoProducerGroup = 5,  // fused kernel: the producer waiting for a group's operand blocks
   kWhoAdder = 6,          // fused kernel: an adder warp waiting for a group's products
-  kWhoProbe = 7           // wait_probe_kernel: the self-test of the bounded wait
+  kWhoProbe = 7,          // wait_probe_kernel: the self-test of the bounded wait
+  kWhoSender = 11         // a sending CTA waiting for a block of columns of C to be complete
 };
 
 // How long a CTA that gives up waits for its producer's outstanding TMA loads to land.
@@ -97,12 +102,17 @@ struct FusedKernelParams {
 };
 
 struct NoFuse {
-  static constexpr bool kOn = false;
+  static constexpr bool kOn = false, kSend = false;
+  struct Params {};
+};
+// The plain product kernel whose last CTAs send finished blocks of C to other GPUs (run_sender).
+struct WithSenders {
+  static constexpr bool kOn = false, kSend = true;
   struct Params {};
 };
 template <int INNER, int ALGO, typename T>
 struct Fuse {
-  static constexpr bool kOn = true;
+  static constexpr bool kOn = true, kSend = false;
   static constexpr int kInner = INNER, kAlgo = ALGO;
   using Elem = T;
   using Params = FusedKernelParams;
@@ -189,6 +199,62 @@ __device__ __forceinline__ void run_adders(const FusedKernelParams& fz, volatile
     ptx::named_bar_sync(1, kAdderThreads);  // all have read the decision before it is written again
     if (!go) break;
     adder_combine<INNER, ALGO, T>(fz.comb, fz.comb_quad[t], first, stride);
+  }
+}
+
+// ---- sending CTAs of a row-sharded dense product -----------------------------------------------
+// The tile order walks the m-tiles of a band, then moves to the next n-tile, so C is finished one
+// block of columns (all rows of a band x the columns of one n-tile) after the other. Every epilogue
+// warp counts its part of a tile on the counter of that block once its TMA stores have reached
+// global memory; a sending CTA waits for a block's counter, reads the block from this GPU's C and
+// writes it to the other copies: one multimem store per 16 bytes when a multicast address is given,
+// else one store per peer. The wait is bounded like every other; all loads read local memory.
+template <int kThreads>
+__device__ __forceinline__ void run_sender(const GemmKernelParams& p, int sender, int n_senders, int tile_m, int tile_n,
+                                           int parts_per_tile, volatile uint32_t* abort_word, volatile uint32_t* go_word) {
+  const int n_bands = (p.m_tiles + p.raster_group - 1) / p.raster_group;
+  const int units = n_bands * p.n_tiles;
+  const int64_t row_bytes = p.ldc * 2;
+  for (int u = sender; u < units; u += n_senders) {
+    const int g = u / p.n_tiles, nt = u - g * p.n_tiles;
+    const int gsz = min(p.raster_group, p.m_tiles - g * p.raster_group);
+    if (threadIdx.x == 0) {
+      const bool ok = ptx::wait_counter(p.send_counters + u, static_cast<uint32_t>(gsz * parts_per_tile), abort_word, kWhoSender);
+      ptx::fence_proxy_async_all();   // the block was written by TMA stores
+      *go_word = ok ? 1u : 0u;
+    }
+    __syncthreads();
+    const bool go = *go_word != 0;
+    __syncthreads();                  // all have read the decision before it is written again
+    if (!go) break;
+    const int r0 = g * p.raster_group * tile_m;
+    const int nrows = min(gsz * tile_m, p.M - r0);
+    const int c0 = nt * tile_n;
+    const int vpr = (min(tile_n, p.N - c0) * 2) / 16;   // 16-byte vectors per row of the block
+    const int total = nrows * vpr;
+    const uint8_t* src = p.dst[0] + static_cast<int64_t>(r0) * row_bytes + static_cast<int64_t>(c0) * 2;
+    const int64_t dst_off = static_cast<int64_t>(r0) * row_bytes + static_cast<int64_t>(c0) * 2;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kThreads) {
+      uint4 v[4];
+      int64_t off[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i0 + k * kThreads;
+        const int row = i / vpr, c = i - row * vpr;
+        off[k] = static_cast<int64_t>(row) * row_bytes + c * 16;
+        if (i < total) v[k] = __ldcg(reinterpret_cast<const uint4*>(src + off[k]));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (i0 + k * kThreads < total) {
+          if (p.mc != nullptr) {
+            ptx::multimem_st_v4(p.mc + dst_off + off[k], v[k]);
+          } else {
+            for (int d = 1; d < p.n_dst; ++d) *reinterpret_cast<uint4*>(p.dst[d] + dst_off + off[k]) = v[k];
+          }
+        }
+      }
+    }
   }
 }
 
@@ -339,13 +405,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(gbase + kStages * STAGE_BYTES + STAGING_BYTES + 8 * (2 * kStages + 4));
   volatile uint32_t* abort_word = tmem_slot + 1;
-  [[maybe_unused]] volatile uint32_t* go_word = tmem_slot + 2;  // fused kernel: the adders' go / stop decision
+  [[maybe_unused]] volatile uint32_t* go_word = tmem_slot + 2;  // go / stop decision of the adders (fused kernel) or of a sending CTA
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / kCtaGroup;
-  const int num_clusters = gridDim.x / kCtaGroup;
+  // clusters that multiply; the sending CTAs of a row-sharded product come after them in the grid
+  const int num_clusters = (static_cast<int>(gridDim.x) - (F::kSend ? p.send_ctas : 0)) / kCtaGroup;
+  [[maybe_unused]] const bool is_sender = F::kSend && cluster_id >= num_clusters;
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
@@ -377,7 +445,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   // Fused kernel: 512 threads start with 128 registers each and re-divide them by warpgroup,
   // 40 (producer, MMA issuer) + 168 + 168 (epilogue) + 136 (adders) per thread.
-  if (warp < kEpiWarp0) {
+  if (is_sender) {
+    if constexpr (F::kSend) {
+      constexpr int kThreadsAll = 64 + 128 * kNH;
+      run_sender<kThreadsAll>(p, (cluster_id - num_clusters) * kCtaGroup + static_cast<int>(cta_rank), p.send_ctas,
+                              kBM * kCtaGroup, BN_TILE, EPI_WARPS * kCtaGroup, abort_word, go_word);
+    }
+  } else if (warp < kEpiWarp0) {
   if constexpr (F::kOn) ptx::setmaxnreg_dec<40>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -390,10 +464,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int tile = cluster_id; alive && tile < p.total_tiles; tile += num_clusters, ++it) {
         int b, mt, nt;
         decode_tile(p, tile, b, mt, nt);
-        // Every other tile of a cluster walks K backwards: it then starts with the K slices its
-        // neighbours in the previous wave touched last, which are the ones still in L2 (walking
-        // forwards every time is the cyclic pattern an LRU cache serves worst).
-        const bool k_reversed = (it & 1) != 0;
+        // Every other wave of tiles walks K backwards: a cluster then starts its next tile with the K
+        // slices its neighbours touched last, which are the ones still in L2 (walking forwards every
+        // time is the cyclic pattern an LRU cache serves worst). A wave is counted in tiles of the
+        // whole device, not of this launch's grid, so the order of the additions along K, and with
+        // it every bit of the result, is the same on any number of SMs.
+        const bool k_reversed = ((tile / p.wave_tiles) & 1) != 0;
         if constexpr (F::kOn) {
           // first tile of a new outer group: every CTA's adders must have stored its operand blocks
           const int g = b / fz.np2;
@@ -551,7 +627,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (lane == 0) ok = ptx::mbar_wait<kCtaGroup == 2, 64>(tfull_bar(buf), aphase, abort_word, kWhoEpilogue) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      if (p.n_dst > 1 && p.stagger) {
+      if (p.n_dst > 1 && p.stagger && !F::kSend) {
         const uint32_t now = static_cast<uint32_t>(ptx::global_timer_ns());  // differences survive the wrap
         if (it > 0) {
           const uint32_t period = now - tile_seen_ns;
@@ -597,7 +673,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           ptx::tma_store_3d_hint(&tmC.m[0], sbuf, col0 + gc, row_warp, b, store_policy);
           ptx::tma_store_commit();
         }
-        if (p.n_dst > 1) {
+        if (p.n_dst > 1 && !F::kSend) {
           // The other copies of C (peer GPUs' memory) get the same box through ordinary 16-byte
           // stores, whole 128-byte rows per quarter warp. They travel through the load/store unit, so
           // a slow NVLink write never sits in the TMA queue in front of the next operand loads.
@@ -672,6 +748,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             ptx::red_release_gpu_add(fz.flags + 8 + b / fz.np2, 1u);
           }
           __syncwarp();
+        }
+        if constexpr (F::kSend) {
+          if (p.send_ctas > 0) {
+            // the same for the sending CTAs: this warp's part of the block of columns is in global memory
+            if (lane == 0) {
+              ptx::tma_store_wait_all<0>();
+              ptx::fence_proxy_async_all();
+              __threadfence();
+              ptx::red_release_gpu_add(p.send_counters + (mt / p.raster_group) * p.n_tiles + nt, 1u);
+            }
+            __syncwarp();
+          }
         }
       } else if (p.tma_store) {
 #pragma unroll 1
@@ -794,7 +882,7 @@ constexpr double kBandBytesInL2 = 72.0 * 1024 * 1024;
 
 template <int kCtaGroup, int kNH, int kStages, bool kTf32, class F>
 int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& tmC, GemmKernelParams kp,
-                   const typename F::Params& fz, int sms, cudaStream_t stream) {
+                   const typename F::Params& fz, int sms, int all_sms, cudaStream_t stream) {
   constexpr int kThreadsV = F::kOn ? 512 : 64 + 128 * kNH;
   constexpr int STAGE_BYTES = kBM * kRowBytes + kNH * (256 / kCtaGroup) * kRowBytes;
   constexpr int STAGING_BYTES = 4 * kNH * (kNH == 1 ? 2 : 1) * 4096;
@@ -814,10 +902,11 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& 
     if (dev < 0 || dev >= 64) return B200S_ERR_NO_DEVICE;
     if (max_clusters[dev] == 0) {
       B200S_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-      int n = sms / kCtaGroup;
+      // all_sms: the capacity of the device, whatever share of it this call may use
+      int n = all_sms / kCtaGroup;
       if (kCtaGroup == 2) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(sms / 2 * 2);
+        cfg.gridDim = dim3(all_sms / 2 * 2);
         cfg.blockDim = dim3(kThreadsV);
         cfg.dynamicSmemBytes = SMEM;
         cudaLaunchAttribute at[1];
@@ -838,7 +927,12 @@ int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CMaps& 
   }
   if (sms / kCtaGroup < resident) resident = sms / kCtaGroup;
 
-  const int clusters = kp.total_tiles < resident ? kp.total_tiles : resident;
+  // sending CTAs (a row-sharded product) come on top of the clusters that multiply
+  const int send_clusters = F::kSend ? kp.send_ctas / kCtaGroup : 0;
+  int clusters = resident - send_clusters;
+  if (clusters < 1) return B200S_ERR_BAD_SHAPE;
+  if (kp.total_tiles < clusters) clusters = kp.total_tiles;
+  clusters += send_clusters;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(clusters * kCtaGroup);
   cfg.blockDim = dim3(kThreadsV);
@@ -861,7 +955,9 @@ struct Prepared {
   CMaps tmC;
   GemmKernelParams kp;
   int variant, sms;
+  int all_sms;          // SMs of the device (sms may be a share of them)
   bool tf32;
+  int send_units = 0;   // counters the sending CTAs wait on (0: no sending CTAs)
 };
 
 // Validates the product, picks the tile variant (forced_variant > 0 overrides), builds the tensor
@@ -950,6 +1046,23 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
   kp.total_tiles = static_cast<int32_t>(total);
   const double band_bytes = static_cast<double>(kRasterGroup) * tile_m * static_cast<double>(g.K) * static_cast<double>(es);
   kp.raster_group = band_bytes <= kBandBytesInL2 ? kRasterGroup : kRasterGroupLongK;
+  const int all_sms = g.sms > 0 ? g.sms : sm_count();
+  kp.wave_tiles = all_sms / cta_group > 0 ? all_sms / cta_group : 1;
+  out->all_sms = all_sms;
+  kp.send_ctas = 0;
+  kp.send_counters = nullptr;
+  if (g.send_sms >= 2 && kp.n_dst > 1) {
+    // Sending CTAs exist for the 256x512 CTA-pair variant with 16-bit output through the TMA-store
+    // epilogue; any other product keeps the exchange in its epilogue.
+    const int64_t units = static_cast<int64_t>((kp.m_tiles + kp.raster_group - 1) / kp.raster_group) * kp.n_tiles;
+    const int send = (g.send_sms & ~1);
+    if (variant == 3 && !tf32 && tma_store && oes == 2 && g.batch == 1 && units <= kSendUnits && sms - send >= 2) {
+      kp.send_counters = device_send_counters();
+      if (!kp.send_counters) return B200S_ERR_NO_DEVICE;
+      kp.send_ctas = send;
+      out->send_units = static_cast<int>(units);
+    }
+  }
   kp.a_mn = g.a_major == B200S_MN_MAJOR;
   kp.b_mn = g.b_major == B200S_MN_MAJOR;
   kp.fmt = tf32 ? 2 : (g.in_dtype == B200S_BF16 ? 1 : 0);
@@ -968,9 +1081,9 @@ int prepare_gemm(const GemmArgs& g, int forced_variant, Prepared* out) {
 template <int INNER, int ALGO>
 int launch_fused_dtype(const Prepared& pr, const FusedKernelParams& fz, int dtype, cudaStream_t stream) {
   if (dtype == B200S_BF16)
-    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __nv_bfloat16>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, stream);
+    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __nv_bfloat16>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, pr.all_sms, stream);
   if (dtype == B200S_FP16)
-    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __half>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, stream);
+    return launch_variant<2, 2, 4, false, Fuse<INNER, ALGO, __half>>(pr.tmA, pr.tmB, pr.tmC, pr.kp, fz, pr.sms, pr.all_sms, stream);
   return B200S_ERR_BAD_DTYPE;
 }
 
@@ -1010,16 +1123,21 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   int rc = prepare_gemm(g, 0, &pr);
   if (rc) return rc;
   const NoFuse::Params none{};
+  if (pr.kp.send_ctas > 0) {
+    const WithSenders::Params none_s{};
+    B200S_CUDA_OK(cudaMemsetAsync(pr.kp.send_counters, 0, sizeof(uint32_t) * static_cast<size_t>(pr.send_units), stream));
+    return launch_variant<2, 2, 4, false, WithSenders>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none_s, pr.sms, pr.all_sms, stream);
+  }
   if (pr.variant == 3) {
-    if (pr.tf32) return launch_variant<2, 2, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
-    return launch_variant<2, 2, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+    if (pr.tf32) return launch_variant<2, 2, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
+    return launch_variant<2, 2, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
   }
   if (pr.variant == 2) {
-    if (pr.tf32) return launch_variant<2, 1, 6, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
-    return launch_variant<2, 1, 6, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+    if (pr.tf32) return launch_variant<2, 1, 6, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
+    return launch_variant<2, 1, 6, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
   }
-  if (pr.tf32) return launch_variant<1, 1, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
-  return launch_variant<1, 1, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, stream);
+  if (pr.tf32) return launch_variant<1, 1, 4, true, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
+  return launch_variant<1, 1, 4, false, NoFuse>(pr.tmA, pr.tmB, pr.tmC, pr.kp, none, pr.sms, pr.all_sms, stream);
 }
 
 int launch_fused(const FusedArgs& f, cudaStream_t stream) {

@@ -173,8 +173,13 @@ class PeerShardedMatmul:
             raise ValueError("at most 8 ranks (one node)")
         if M % self.world:
             raise ValueError("M must be a multiple of the number of ranks")
-        if exchange not in ("auto", "store", "multicast", "copy", "push", "overlap"):
-            raise ValueError("exchange must be 'auto', 'store', 'multicast', 'overlap', 'push' or 'copy'")
+        if exchange not in ("auto", "store", "multicast", "senders", "copy", "push", "overlap"):
+            raise ValueError("exchange must be 'auto', 'store', 'multicast', 'senders', 'overlap', 'push' or 'copy'")
+        # 'senders': as 'auto', but push_sms CTAs of the product kernel do the remote stores, block of
+        # columns by block of columns as C gets finished, instead of the epilogue warps of all CTAs
+        self.sender_sms = 0
+        if exchange == "senders":
+            self.sender_sms, exchange = int(push_sms), "auto"
         if exchange == "overlap" and panels < 2:
             panels = 4                       # the last panel's transfer is the part that is not hidden
         self.M, self.N, self.K, self.dtype = M, N, K, dtype
@@ -313,6 +318,20 @@ class PeerShardedMatmul:
         self._barrier(stream)                # every rank is done with the previous contents of C
         if self.exchange == "overlap":
             return self._overlapped(A_block, B, stream)
+        senders_before = lib.b200s_set_sender_sms(self.sender_sms) if self.sender_sms else 0
+        try:
+            self._panels(A_block, B, stream, lib, ops)
+        finally:
+            if self.sender_sms:
+                lib.b200s_set_sender_sms(senders_before)
+        for cs in self.copy_streams:
+            stream.wait_stream(cs)
+        self._barrier(stream)                # every rank's stores have been issued and completed
+        return self.C
+
+    def _panels(self, A_block, B, stream, lib, ops):
+        import ctypes
+
         for i in range(self.panels):
             p0 = i * self.prow
             a_panel = A_block[p0:p0 + self.prow]
@@ -358,7 +377,3 @@ class PeerShardedMatmul:
                         with torch.cuda.stream(cs):
                             peer_rows = self.hdl.get_buffer(r, (self.prow, self.N), self.dtype, row0 * self.N)
                             peer_rows.copy_(c_rows, non_blocking=True)
-        for cs in self.copy_streams:
-            stream.wait_stream(cs)
-        self._barrier(stream)                # every rank's stores have been issued and completed
-        return self.C

@@ -31,7 +31,7 @@ def main():
     r0, r1 = row_block(M, world, rank)
     failures = []
     for algo, depth, panels in (("classic", 2, 2), ("dense", 0, 1), ("classic", 1, 1), ("auto", -1, 2)):
-        for exchange in ("store", "multicast", "overlap", "push", "copy"):    # multicast falls back to store without NVLS
+        for exchange in ("store", "multicast", "senders", "overlap", "push", "copy"):    # multicast falls back to store without NVLS
             plan = PeerShardedMatmul(M, N, K, torch.bfloat16, algo=algo, depth=depth, panels=panels, exchange=exchange,
                                      barrier_ms=5000)
             for _ in range(2):              # the second call overwrites a C the peers have already read
