@@ -96,3 +96,29 @@ def test_stage_timing_covers_the_call(lib, fuse):
     with ops.stage_timing(2) as none:                   # the multi-stream schedule records nothing
         ops.matmul_out(A, B, C, algo="classic", depth=2, fuse=2, pipeline=1)
     assert none["calls"] == 0
+
+
+@pytest.mark.parametrize("algo,depth", [("dense", 0), ("classic", 2)])
+def test_result_does_not_depend_on_how_many_sms_the_products_get(built_library, algo, depth):
+    """b200s_set_product_sms leaves SMs to other kernels. More tiles than CTAs, so the tiles are
+    dealt out differently on fewer SMs; the order of the additions along K is tied to the tile, not
+    to the CTA that happens to run it, so every bit stays the same."""
+    if not torch.cuda.is_available():
+        pytest.fail("this test needs a CUDA device")
+    from strassen_triton_b200 import _lib, ops
+
+    lib = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    M, N, K = (4096, 4096, 2048) if depth == 0 else (8192, 8192, 4096)
+    A = (torch.randn(M, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    B = (torch.randn(K, N, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    full = ops.matmul(A, B, algo=algo, depth=depth, pipeline=2, fuse=2)
+    assert lib.b200s_set_product_sms(96) == 0
+    try:
+        fewer = ops.matmul(A, B, algo=algo, depth=depth, pipeline=2, fuse=2)
+        assert lib.b200s_set_product_sms(30) == 96
+        fewest = ops.matmul(A, B, algo=algo, depth=depth, pipeline=2, fuse=2)
+    finally:
+        lib.b200s_set_product_sms(0)
+    assert torch.equal(fewer, full) and torch.equal(fewest, full)
+    assert ops.device_status() == (0, 0)
