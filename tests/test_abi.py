@@ -213,6 +213,8 @@ def test_new_entry_points_validate_before_touching_a_device(lib):
     assert lib.b200s_push_panel(24, None, 0, 32, 256, 8, None) == _lib.ERR_BAD_ALIGNMENT
     assert lib.b200s_set_product_sms(-1) == _lib.ERR_BAD_SHAPE
     assert lib.b200s_set_product_sms(140) == 0 and lib.b200s_set_product_sms(0) == 140        # returns the previous setting
+    assert lib.b200s_set_sender_sms(-2) == _lib.ERR_BAD_SHAPE and lib.b200s_set_sender_sms(66) == _lib.ERR_BAD_SHAPE
+    assert lib.b200s_set_sender_sms(8) == 0 and lib.b200s_set_sender_sms(0) == 8
 
 
 def test_fused_schedule_keeps_its_counters_at_the_end_of_the_scratch(lib):
