@@ -374,19 +374,22 @@ def verify_sharded(plan, B, n, world, rank, dev, dist):
     owners = sorted({(rank + 1) % world, (rank + world // 2) % world} - {rank})
     rows_checked, exact = 0, True
     probe_err = 0.0
+    layout = [None] * world       # every rank's first row, rows, row panels and algorithm
+    dist.all_gather_object(layout, (plan.row_start, plan.rows, plan.panels, plan.algo, plan.depth))
     for owner in owners:
-        r0, r1 = row_block(n, world, owner)
+        r0, rows_o, panels_o, algo_o, depth_o = layout[owner]
+        r1, prow = r0 + rows_o, rows_o // panels_o
         A_owner, _ = seeded_inputs(r1 - r0, n, "normal", 0, dev, row_offset=r0, want_b=False)
-        for pi in sorted({0, plan.panels - 1}):
-            p0 = pi * plan.prow
-            want = plan.panel_product(A_owner[p0:p0 + plan.prow], B)
-            got = C[r0 + p0: r0 + p0 + plan.prow]
+        for pi in sorted({0, panels_o - 1}):
+            p0 = pi * prow
+            want = plan.panel_product(A_owner[p0:p0 + prow], B, algo_o, depth_o)
+            got = C[r0 + p0: r0 + p0 + prow]
             exact = exact and bool(torch.equal(got, want))
-            rows_checked += plan.prow
+            rows_checked += prow
             if owner == owners[0] and pi == 0:
                 # C x = A (B x) in fp64 on the first rows of this panel
                 x = torch.randn(n, 1, device=dev, dtype=torch.float64)
-                k = min(plan.prow, 2048)
+                k = min(prow, 2048)
                 ref = A_owner[p0:p0 + k].double() @ _b_times_x(B, x)
                 probe_err = ((got[:k].double() @ x - ref).norm() / ref.norm()).item()
         del A_owner
@@ -475,19 +478,46 @@ def run_gpu_arm(args):
                                       workspace=ws)
     else:
         n = 32768
+        balance = None
         r0, r1 = row_block(n, world, rank)
         A, B = seeded_inputs(r1 - r0, n, "normal", 0, dev, row_offset=r0)
         if args.exchange.startswith("peer"):
-            from strassen_triton_b200.sharded import PeerShardedMatmul
+            from strassen_triton_b200.sharded import PeerShardedMatmul, balanced_row_counts
 
-            plan = PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
-                                     panels=args.panels, device=dev,
-                                     exchange={"peer": "auto", "peer_store": "store", "peer_multicast": "multicast",
-                                               "peer_push": "push", "peer_copy": "copy", "peer_overlap": "overlap",
-                                               "peer_senders": "senders"}[args.exchange],
-                                     push_sms=args.push_sms)
+            def make_plan(row_counts=None):
+                return PeerShardedMatmul(n, n, n, torch.bfloat16, algo=args.algo, depth=-1 if args.algo == "auto" else depth,
+                                         panels=args.panels, device=dev,
+                                         exchange={"peer": "auto", "peer_store": "store", "peer_multicast": "multicast",
+                                                   "peer_push": "push", "peer_copy": "copy", "peer_overlap": "overlap",
+                                                   "peer_senders": "senders"}[args.exchange],
+                                         push_sms=args.push_sms, row_counts=row_counts)
+
+            plan = make_plan()
             C = plan.C
             step = lambda: plan(A, B)  # noqa: E731
+            if args.balance:
+                # The GPUs of a box differ in sustained speed under the power cap and the step ends with the
+                # slowest: time every rank's own kernels on equal blocks, then hand out rows by speed.
+                for _ in range(2):
+                    step()
+                torch.cuda.synchronize()
+                with ops.stage_timing(16) as own:
+                    for _ in range(3):
+                        step()
+                    torch.cuda.synchronize()
+                own_ms = sum(own[k] for k in ops.STAGES) * max(own["calls"], 1) / 3.0
+                mine = torch.tensor([own_ms], device=dev, dtype=torch.float64)
+                everyone = [torch.zeros_like(mine) for _ in range(world)]
+                dist.all_gather(everyone, mine)
+                times_ms = [t.item() for t in everyone]
+                counts = balanced_row_counts(n, times_ms, plan.row_counts)
+                balance = {"own_kernel_ms_on_equal_blocks": [round(t, 3) for t in times_ms], "rows": counts}
+                if counts != plan.row_counts:
+                    del plan
+                    plan = make_plan(counts)
+                    C = plan.C
+                    r0, r1 = plan.row_start, plan.row_start + plan.rows
+                    A, _ = seeded_inputs(r1 - r0, n, "normal", 0, dev, row_offset=r0, want_b=False)
         else:
             C = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
             p, _, _ = ops.make_problem(A, B, C[r0:r1], args.algo, -1 if args.algo == "auto" else depth)
@@ -549,8 +579,7 @@ def run_gpu_arm(args):
         def e2e_step():             # B, then A in row panels; products and C's way back overlap the arrivals
             streamed(hA, hB, hC)
     else:
-        r0, r1 = row_block(n, world, rank)
-        hC = torch.empty((r1 - r0, n), dtype=torch.bfloat16, pin_memory=True)
+        hC = torch.empty((r1 - r0, n), dtype=torch.bfloat16, pin_memory=True)    # r0, r1: this rank's rows
 
         def e2e_step():
             dA = hA.to(dev, non_blocking=True)
@@ -613,6 +642,12 @@ def run_gpu_arm(args):
                                               "block of columns by block of columns as C gets finished (no collective in the "
                                               "timed path)")
             line["config"]["panels"] = plan.panels if plan is not None else args.panels
+            if balance is not None:
+                line["config"]["row_blocks"] = {"rows_per_rank": balance["rows"],
+                                                "own_kernel_ms_on_equal_blocks": balance["own_kernel_ms_on_equal_blocks"],
+                                                "how": "after 5 steps on equal blocks every rank's block is sized by the speed "
+                                                       "its GPU showed, in units of 256 rows (the GPUs of a box differ under "
+                                                       "the power cap, and a strong-scaling step ends with the slowest)"}
             if plan is not None:
                 line["config"]["per_rank"] = {"algo": plan.algo, "depth": plan.depth,
                                               "shape": [plan.prow, n, n], "from": ("flag" if args.algo != "auto" else
@@ -762,6 +797,9 @@ def main():
                          "the row blocks")
     ap.add_argument("--push-sms", type=int, default=8, help="N > 1, --exchange peer_overlap: SMs left to the kernel that sends "
                                                             "a finished row panel while the next one is multiplied")
+    ap.add_argument("--balance", type=int, default=0, help="N > 1, peer exchanges: 1 = after a few steps on equal row blocks, "
+                                                            "size every rank's block by the speed its GPU showed (0 = equal blocks; "
+                                                            "measured: the GPUs' order changes from run to run and nothing is gained)")
     ap.add_argument("--fsdp", type=int, default=1, help="N > 1: also time the FSDP GPT-2 step (0 = skip)")
     ap.add_argument("--quick", action="store_true", help="N = 1: skip the comparison arms (for a launch list under ncu)")
     ap.add_argument("--only", default=None, help="run one kernel a few times and exit: gemm_grouped, cublas_grouped, "

@@ -128,6 +128,27 @@ def _all_gather_uneven(views, mine, group):
         dist.broadcast(v, src=dist.get_global_rank(group, r) if group is not None else r, group=group)
 
 
+def balanced_row_counts(M: int, seconds_per_rank, rows_per_rank, quantum: int = 256):
+    """Rows for every rank in proportion to the speed it showed (rows_per_rank[r] rows took
+    seconds_per_rank[r]), in multiples of ``quantum``, adding up to M; at least one quantum each.
+    A strong-scaling step ends with the slowest GPU, and the GPUs of a box differ under a power cap."""
+    world = len(seconds_per_rank)
+    if world != len(rows_per_rank) or M % quantum or M // quantum < world:
+        raise ValueError("cannot split M into quanta over the ranks")
+    speed = [max(r, 1) / max(t, 1e-9) for r, t in zip(rows_per_rank, seconds_per_rank)]
+    units = M // quantum
+    ideal = [units * v / sum(speed) for v in speed]
+    counts = [max(1, int(x)) for x in ideal]
+    # hand the remaining quanta to the ranks furthest below their share (largest remainder)
+    while sum(counts) < units:
+        r = max(range(world), key=lambda i: ideal[i] - counts[i])
+        counts[r] += 1
+    while sum(counts) > units:
+        r = max((i for i in range(world) if counts[i] > 1), key=lambda i: counts[i] - ideal[i])
+        counts[r] -= 1
+    return [c * quantum for c in counts]
+
+
 class PeerShardedMatmul:
     """Row-sharded C = A @ B whose exchange rides on the product kernels.
 
@@ -158,7 +179,7 @@ class PeerShardedMatmul:
 
     def __init__(self, M: int, N: int, K: int, dtype=torch.bfloat16, group=None, algo: str = "auto",
                  depth: int = -1, panels: int = 1, device=None, exchange: str = "auto", barrier_ms: float = 2000.0,
-                 push_sms: int = 8):
+                 push_sms: int = 8, row_counts=None):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -171,8 +192,17 @@ class PeerShardedMatmul:
         self.rank = dist.get_rank(self.group)
         if self.world > 8:
             raise ValueError("at most 8 ranks (one node)")
-        if M % self.world:
-            raise ValueError("M must be a multiple of the number of ranks")
+        # Rows of A (and of C) per rank: equal blocks unless the caller hands out others, for instance
+        # fewer rows to GPUs that measured slower (balanced_row_counts); every rank must pass the same list.
+        if row_counts is None:
+            if M % self.world:
+                raise ValueError("M must be a multiple of the number of ranks")
+            row_counts = [M // self.world] * self.world
+        row_counts = [int(r) for r in row_counts]
+        if len(row_counts) != self.world or sum(row_counts) != M or min(row_counts) <= 0:
+            raise ValueError("row_counts must give every rank a positive number of rows adding up to M")
+        self.row_counts = row_counts
+        self.row_starts = [sum(row_counts[:r]) for r in range(self.world)]
         if exchange not in ("auto", "store", "multicast", "senders", "copy", "push", "overlap"):
             raise ValueError("exchange must be 'auto', 'store', 'multicast', 'senders', 'overlap', 'push' or 'copy'")
         # 'senders': as 'auto', but push_sms CTAs of the product kernel do the remote stores, block of
@@ -184,7 +214,8 @@ class PeerShardedMatmul:
             panels = 4                       # the last panel's transfer is the part that is not hidden
         self.M, self.N, self.K, self.dtype = M, N, K, dtype
         self.exchange = exchange
-        self.rows = M // self.world
+        self.rows = self.row_counts[self.rank]
+        self.row_start = self.row_starts[self.rank]
         self.device = torch.device(device if device is not None else torch.cuda.current_device())
         if algo == "auto" and self.world >= 4:
             # The tuner table is measured on one GPU, where a Strassen block is a few per cent ahead of
@@ -249,10 +280,12 @@ class PeerShardedMatmul:
         self._lib.check(self._lib.load().b200s_peer_barrier(self._pads, self.rank, self.world, self._epoch,
                                                             self._limit_ns, stream.cuda_stream))
 
-    def panel_product(self, a_panel: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
-        """The product of one row panel as this plan computes it, into fresh local memory: the same
-        kernels and arithmetic as the exchanged panel, for checking what arrived bit for bit."""
-        return self._ops.matmul(a_panel, B, algo=self.algo, depth=self.depth, pipeline=2, fuse=2)
+    def panel_product(self, a_panel: torch.Tensor, B: torch.Tensor, algo=None, depth=None) -> torch.Tensor:
+        """The product of one row panel as this plan computes it (or as another rank's plan does, given
+        its algorithm and depth), into fresh local memory: the same kernels and arithmetic as the
+        exchanged panel, for checking what arrived bit for bit."""
+        return self._ops.matmul(a_panel, B, algo=self.algo if algo is None else algo,
+                                depth=self.depth if depth is None else depth, pipeline=2, fuse=2)
 
     def _overlapped(self, A_block: torch.Tensor, B: torch.Tensor, stream) -> torch.Tensor:
         """Row panels one after the other into this rank's own rows of C, each on all SMs but
@@ -268,7 +301,7 @@ class PeerShardedMatmul:
         try:
             for i in range(self.panels):
                 p0 = i * self.prow
-                row0 = self.rank * self.rows + p0
+                row0 = self.row_start + p0
                 c_rows = self.C[row0: row0 + self.prow]
                 prob, a2, b2 = ops.make_problem(A_block[p0:p0 + self.prow], B, c_rows, self.algo, self.depth, pipeline=2,
                                                 fuse=2, b_blocks_ready=i > 0 and self.depth > 0)
@@ -335,7 +368,7 @@ class PeerShardedMatmul:
         for i in range(self.panels):
             p0 = i * self.prow
             a_panel = A_block[p0:p0 + self.prow]
-            row0 = self.rank * self.rows + p0
+            row0 = self.row_start + p0
             c_rows = self.C[row0: row0 + self.prow]
             prob, a2, b2 = ops.make_problem(a_panel, B, c_rows, self.algo, self.depth, pipeline=2, fuse=2,
                                             b_blocks_ready=i > 0 and self.depth > 0)

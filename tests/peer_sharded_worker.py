@@ -43,6 +43,18 @@ def main():
                 bad = (C != want).any(dim=1).nonzero().flatten()
                 failures.append(f"{algo}/{depth}/{panels}/{exchange}: {bad.numel()} rows differ, first {bad[:4].tolist()}")
             del plan
+    # unequal row blocks (a slower GPU gets fewer rows): rank r takes 768, 1280, 768, 1280, ... rows
+    counts = [768 if r % 2 == 0 else 1280 for r in range(world)]
+    for algo, depth in (("dense", 0), ("classic", 1)):
+        plan = PeerShardedMatmul(M, N, K, torch.bfloat16, algo=algo, depth=depth, row_counts=counts, barrier_ms=5000)
+        s0 = plan.row_start
+        for _ in range(2):
+            C = plan(A[s0:s0 + plan.rows], B)
+        plan.check()
+        want = torch.cat([plan.panel_product(A[plan.row_starts[r]:plan.row_starts[r] + counts[r]], B) for r in range(world)])
+        if plan.panels != 1 or not torch.equal(C, want):
+            failures.append(f"unequal row blocks, {algo}/{depth}: differs")
+        del plan
     C = sharded_matmul(A[r0:r1], B, M, panels=2, algo="classic", depth=2)
     rows = (r1 - r0) // 2
     want = torch.cat([ops.matmul(A[i * rows:(i + 1) * rows], B, algo="classic", depth=2) for i in range(M // rows)])

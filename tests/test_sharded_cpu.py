@@ -92,3 +92,20 @@ def test_rank_failure_surfaces_as_an_error_not_a_hang():
     status = {r[0]: r[1] for r in results}
     assert status[1] == "error"
     assert status[0] in ("error", "ok")  # gloo may also complete rank 0's send side first
+
+
+def test_balanced_row_counts():
+    from strassen_triton_b200.sharded import balanced_row_counts as b
+
+    assert b(32768, [7.0] * 8, [4096] * 8) == [4096] * 8                       # equal speed: equal blocks
+    got = b(32768, [13.4, 11.1, 12.0, 11.5], [8192] * 4)
+    assert sum(got) == 32768 and all(r % 256 == 0 for r in got)
+    assert got[0] == min(got) and got[1] == max(got)                          # the slowest GPU gets the fewest rows
+    # after the split the predicted times are closer together than before
+    before = max(13.4, 11.1, 12.0, 11.5) / min(13.4, 11.1, 12.0, 11.5)
+    after = [t / 8192 * r for t, r in zip([13.4, 11.1, 12.0, 11.5], got)]
+    assert max(after) / min(after) < before
+    assert b(1024, [1.0, 100.0], [512, 512]) == [768, 256]                    # nobody is left without rows
+    import pytest
+    with pytest.raises(ValueError):
+        b(1000, [1.0, 1.0], [500, 500])
