@@ -159,9 +159,16 @@ class PeerShardedMatmul:
     from its recombination kernel - plain stores over NVLink, tile by tile, no all-gather pass and no
     staging copy; every load reads local memory. ``exchange="multicast"`` (dense panels, NVLS systems)
     stores each tile once to the allocation's multicast address and lets the NVSwitch replicate it,
-    so a rank sends its rows once instead of once per peer. ``exchange="push"`` / ``"copy"`` instead
-    write the panel into the local C and send the finished rows with a small copy kernel or the copy
-    engines.
+    so a rank sends its rows once instead of once per peer. Alternatives kept beside it, all with the
+    same result bits: ``"senders"`` (``push_sms`` CTAs of the dense product kernel multiply nothing and
+    send finished blocks of columns of C while the others multiply), ``"overlap"`` (row panels; a
+    small kernel on a side stream sends panel i from ``push_sms`` SMs while panel i+1 is multiplied on
+    the others), ``"push"`` / ``"copy"`` (the panel goes into the local C first, then a copy kernel or
+    the copy engines send the finished rows).
+
+    ``row_counts`` gives the ranks row blocks of unequal height (the same list on every rank;
+    ``balanced_row_counts`` derives one from measured speeds); rank r then owns rows
+    ``row_starts[r] : row_starts[r] + row_counts[r]`` of A and C.
 
     Algorithm and depth of a panel come from the library's tuner table for the per-rank shape unless
     given (at eight ranks a 4096 x 32768 x 32768 panel is a dense product: with B replicated its
