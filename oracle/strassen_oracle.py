@@ -203,6 +203,17 @@ def _signed_sum(coefs, blocks):
     return acc
 
 
+def recombine(products, depth: int, algo: str = "classic") -> torch.Tensor:
+    """C from the 7^depth product blocks (index p = 7*p1 + p2) by the recombination table: the
+    post-additions and quadrant assembly of fixed_strassen_fp32_agg.py:47-56 and :115-123, in the
+    dtype of the blocks (pass fp64 blocks for a rounding-free reference)."""
+    _, _, W = tables(algo, depth)
+    blocks = list(products)
+    if len(blocks) != 7 ** depth:
+        raise ValueError(f"{7 ** depth} product blocks expected, got {len(blocks)}")
+    return _unblocks([_signed_sum(W[r], blocks) for r in range(4 ** depth)], depth)
+
+
 def library_model(A: torch.Tensor, B: torch.Tensor, depth: int, algo: str = "classic",
                   prod_dtype: Optional[torch.dtype] = None, out_dtype: Optional[torch.dtype] = None,
                   exact_products: bool = True) -> torch.Tensor:

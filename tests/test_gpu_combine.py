@@ -65,9 +65,7 @@ def test_recombination_is_position_wise(lib, algo, prod_dtype, out_dtype, Mb, Nb
     # and the sums are the right ones: fp64 recombination of the same blocks
     from oracle import strassen_oracle as so
 
-    _, _, W = so.tables(algo, 2)
-    prods = [blocks[i].double().cpu() for i in range(49)]
-    want = so._unblocks([so._signed_sum(W[r], prods) for r in range(16)], 2)
+    want = so.recombine([blocks[i].double().cpu() for i in range(49)], 2, algo)
     if beta:
         want = want + c0.double().cpu()
     err = ((wide.double().cpu() - want).norm() / want.norm()).item()

@@ -113,3 +113,24 @@ def test_rectangular_restatement():
     B = torch.randn(160, 64, generator=g)
     C = so.n_layers(A, B, 2, torch.float32, True, True)
     assert so.errors_vs_fp64(C, A, B)[1] < 1e-5
+
+
+def test_recombine_is_the_table_walk_of_the_model():
+    """recombine() on exact products gives A @ B: the tables close (U, V, W of both algorithms, one
+    and two levels), and it is the same sum library_model forms."""
+    import torch
+
+    from oracle import strassen_oracle as so
+
+    g = torch.Generator().manual_seed(3)
+    A = torch.randint(-3, 4, (16, 8), generator=g).double()
+    B = torch.randint(-3, 4, (8, 12), generator=g).double()
+    for algo in ("classic", "winograd"):
+        for depth in (1, 2):
+            U, V, _ = so.tables(algo, depth)
+            ab, bb = so._blocks(A, depth), so._blocks(B, depth)
+            prods = [so._signed_sum(U[p], ab) @ so._signed_sum(V[p], bb) for p in range(7 ** depth)]
+            assert torch.equal(so.recombine(prods, depth, algo), A @ B)
+    import pytest
+    with pytest.raises(ValueError):
+        so.recombine([A] * 3, 1)
