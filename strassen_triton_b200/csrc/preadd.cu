@@ -109,7 +109,9 @@ int launch_side(const PreaddArgs& a, cudaStream_t stream) {
 // run-time argument; the inner level stays compile-time.
 
 template <int INNER, int ALGO, int SIDE, typename T>
-__global__ void __launch_bounds__(256, 3) preadd_outer_kernel(const PreaddOuterParams p) {
+// (two blocks per SM for the two-level Winograd table, whose sums need more than the 85 registers three would leave)
+__global__ void __launch_bounds__(256, (INNER == 1 && ALGO == sched::kWinograd) ? 2 : 3)
+    preadd_outer_kernel(const PreaddOuterParams p) {
   using OP = OuterPosition<INNER, ALGO, SIDE, T>;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= p.rows_blk * p.cols_vec) return;
